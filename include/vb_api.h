@@ -472,6 +472,10 @@ int vb_codec_attn_chunk(float* d_out, const float* d_qkv, float* d_cache, int64_
  * group_bytes * g further in d_w_tiles (matrices stacked along N) and / or its k-blocks lie group_kb * g + kb_base further
  * inside rows of w_kb_stride k-blocks (matrices stacked along K; 0 = ceil(K / 64)).  mode 0: bf16 [T][ldy] after `act`
  * (as vb_gemm_bf16); mode 1: fp32 [T][ldy]; mode 2: silu(gate) * up, bf16 [T][ldy]. */
+/* vb_gemm_bf16 mode 2 with the clamped gated epilogue: g = min(gate, limit), u = clamp(up, -limit, limit),
+ * y = bf16(g * sigmoid(slope * g) * (u + 1)) */
+int vb_gemm_bf16_glu(void* d_y, const void* d_w_tiles, const void* x_map, int T, int N, int K, int ldy, int tile_rows,
+                     int n_out, float limit, float slope, void* stream);
 int vb_gemm_bf16_grouped(void* d_y, const void* d_w_tiles, const void* x_map, int T, int N, int K, int ldy, int mode,
                          int tile_rows, int n_out, int t_tile, const int32_t* d_tile_group, long long group_bytes,
                          int w_kb_stride, int group_kb, int kb_base, int act, void* stream);
@@ -495,7 +499,14 @@ int vb_gemm_bf16_grouped(void* d_y, const void* d_w_tiles, const void* x_map, in
  *                           group g owns rows row_off[g]..row_off[g+1] (T = upper bound of a group's rows), src(r) =
  *                           gather ? gather[r] : r.  epilogue 1: W = N gate rows then N up rows, Y = silu(gate) * up */
 int vb_embed_rows_f32(float* d_out, const void* d_table, const int32_t* d_ids, int T, int width, int vocab, int dtype,
-                      const void* d_pos_table, const int32_t* d_pos, int n_pos, void* stream);
+                      const void* d_pos_table, const int32_t* d_pos, int n_pos, float scale, float* d_out2, void* stream);
+/* (the table rows are multiplied by `scale` in fp32; d_out2 (optional) receives a second copy of the rows)
+ * vb_gated_residual_norm_f32: the tail of a pre-norm sublayer with a gated residual, in place on the fp32 rows:
+ *   x[t] += sigmoid(r[t] + bias) * y[t] (r [T][ld_r] fp32, bias [width]; r NULL: x += y); x[t] += add[t] (optional);
+ *   out[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w (optional, bf16 or fp32) */
+int vb_gated_residual_norm_f32(float* d_x, const float* d_y, const float* d_r, int ld_r, const float* d_bias,
+                               const float* d_add, void* d_out, const float* d_w, int T, int width, float eps, int out_dtype,
+                               void* stream);
 int vb_rmsnorm2_f32(void* d_out1, void* d_out2, const float* d_x, const float* d_w1, const float* d_w2,
                     const int32_t* d_rows, int T, int width, float eps, int out_dtype, void* stream);
 int vb_residual_side_f32(float* d_x, const float* d_y1, const float* d_y2, float mult, const void* d_side_gate,
@@ -510,8 +521,9 @@ int vb_postnorm_residual_f32(float* d_x, const float* d_y, int y_planes, const f
                              void* stream);
 int vb_linear(void* d_out, const void* d_x, const void* d_w, int T, int N, int K, int ldx, int ldo, int in_dtype,
               int out_dtype, int epilogue, float alpha, const int32_t* d_row_off, const int32_t* d_gather, int groups,
-              long long w_group_stride, void* stream);
-/* (vb_linear epilogues 2, 3, 4: relu(y)^2, gelu (erf), gelu (tanh).)
+              long long w_group_stride, float glu_limit, float glu_slope, void* stream);
+/* (vb_linear epilogues 2, 3, 4: relu(y)^2, gelu (erf), gelu (tanh).  Epilogue 1 with glu_limit > 0 is the clamped gated
+ * form: g = min(gate, limit), u = clamp(up, -limit, limit), Y = g * sigmoid(glu_slope * g) * (u + 1).)
  * vb_linear_batched: `groups` independent products that share their rows (the heads of a token side by side): group g reads
  * X + g * x_group_stride, W + g * w_group_stride and writes Y + g * o_group_stride, all with T rows; with d_gate,
  * Y[r][n] *= sigmoid(d_gate[r * ld_gate + g]).  Epilogues 0, 2, 3, 4. */
@@ -536,7 +548,29 @@ int vb_sum_planes_f32(float* d_out, const float* d_partials, int planes, long lo
  *                       ignore the flag.  Key and value caches that are ONE tensor of equal head sizes are staged once.
  * vb_window_attn_tiled: the same result for prompt portions: tile i covers rows tile_row0[i].. (at most
  *                       vb_window_attn_tile_rows()) of request tile_req[i], whose rows are consecutive positions */
-int vb_rotary_table(float* d_cs, const int32_t* d_pos, const double* d_freq, int T, int half, void* stream);
+int vb_rotary_table(float* d_cs, const int32_t* d_pos, const double* d_freq, int T, int half, double mult, void* stream);
+/* (cos and sin are multiplied by `mult` before they are rounded.)
+ * vb_qkv_norm_rotary_append: like vb_qkv_rotary_append for heads that are RMS-normed over their dim values before the
+ *   rotation (d_q_norm / d_k_norm [dim], shared by all heads; NULL: no norm); layout 0 rotates pairs (2i, 2i + 1), layout 1
+ *   pairs (i, i + half).  Hq query heads, Gk key heads [pages][page][Gk][dim], Gv value heads [pages][page][Gv][vdim]
+ *   (attention with several score maps per head counts every map as a head: Gk = maps * Gv).
+ * vb_latent_rope_append: tail of a fused (queries | latent + shared rotated key part) projection: heads of `dim` unrotated +
+ *   `rot` rotated dims.  The latent is RMS-normed (d_wc) and appended with the rotated key part as ONE row [kv_rank | rot]
+ *   of d_cache; the queries' unrotated parts go to d_q_out [T][H][dim], their rotated parts to
+ *   d_q_lat[t][h][kv_rank .. kv_rank + rot) (the latent-space part in front is filled by vb_linear_batched).
+ * vb_head_pair_combine: d_a fp32 [T][2H][vdim] laid out per group of R heads as [first map of the R heads | second map]:
+ *   o = a1 - lambda * a2, o / sqrt(mean(o^2) + eps) * post * sigmoid(gate) -> d_out [T][H][vdim] (bf16 or fp32) */
+int vb_qkv_norm_rotary_append(const float* d_proj, int ldp, int q_off, int k_off, int v_off, const float* d_cs, int half,
+                              int layout, const float* d_q_norm, const float* d_k_norm, float eps, void* d_q_out,
+                              void* d_k_cache, void* d_v_cache, const int32_t* d_row_req, const int32_t* d_pos,
+                              const int32_t* d_page_indptr, const int32_t* d_page_indices, int page_size, int T, int Hq, int Gk,
+                              int Gv, int dim, int vdim, int dtype, void* stream);
+int vb_latent_rope_append(const float* d_proj, int ldp, int q_off, int c_off, int H, int dim, int rot, int kv_rank,
+                          const float* d_wc, const float* d_cs, int half, int layout, void* d_q_out, void* d_q_lat,
+                          void* d_cache, const int32_t* d_row_req, const int32_t* d_pos, const int32_t* d_page_indptr,
+                          const int32_t* d_page_indices, int page_size, int T, float eps, int dtype, void* stream);
+int vb_head_pair_combine(void* d_out, const float* d_a, const float* d_gate, int ld_gate, int T, int H, int R, int vdim,
+                         float lambda, float post, float eps, int dtype, void* stream);
 int vb_qkv_rotary_append(const float* d_proj, int ldp, int q_off, int k_off, int v_off, const float* d_cs, int half,
                          void* d_q_out, void* d_k_cache, void* d_v_cache, const int32_t* d_row_req, const int32_t* d_pos,
                          const int32_t* d_page_indptr, const int32_t* d_page_indices, int page_size, int T, int H, int G,
@@ -554,13 +588,30 @@ int vb_window_attn(void* d_out, const void* d_q, const void* d_k_cache, const vo
                    int ld_gate, const int32_t* d_row_req, const int32_t* d_pos, const int32_t* d_page_indptr,
                    const int32_t* d_page_indices, int T, int H, int G, int dim, int vdim, int page_size, int window,
                    float scale, int dtype, float* d_part, long long part_floats, const int32_t* d_row_list, int head_rows,
-                   void* stream);
+                   int chunk, int k_ld, int v_ld, int v_share, int out_f32, void* stream);
+/* (chunk > 0: a position sees only the keys of its own block of `chunk` positions, counted from position 0.  k_ld / v_ld:
+ * elements per token of the key / value cache (<= 0: G * dim, (G / v_share) * vdim); a value that is a leading slice of
+ * the single key head has v_ld = k_ld and the same base pointer.  v_share consecutive key heads read one value head.
+ * out_f32: the output is fp32 [T][H * vdim] whatever the operand type.) */
 int vb_window_attn_tile_rows(void);
 int vb_window_attn_tiled(void* d_out, const void* d_q, const void* d_k_cache, const void* d_v_cache, const float* d_gate,
                          int ld_gate, const int32_t* d_pos, const int32_t* d_page_indptr, const int32_t* d_page_indices,
                          const int32_t* d_qo_indptr, const int32_t* d_tile_req, const int32_t* d_tile_row0, int n_tiles,
                          int T, int H, int G, int dim, int vdim, int page_size, int window, float scale, int dtype,
-                         void* stream);
+                         int chunk, int k_ld, int v_ld, int v_share, int out_f32, void* stream);
+/* Element-wise gated recurrence (minGRU) over fp32 state slots [slots][width]: z = sigmoid(pz + bz), u = px + bx,
+ * c = u + 1/2 (u >= 0) or sigmoid(u), S_t = (1 - z) S_(t-1) + z c (S = 0 before position 0), out = S_t * silu(pg); pz, px,
+ * pg are columns z_off, x_off, g_off of the fp32 projection rows.  single_rows / multi_rows select the requests served.
+ * vb_mingru_tiled: prompt portions as tiles of tile_rows rows (tile i = rows tile_row0[i].. of request tile_req[i], in
+ * request order; single-row requests have none): tile summaries, a scan over each request's tiles, outputs per tile;
+ * d_scratch fp32 [n_tiles][2][width] */
+int vb_mingru(void* d_out, float* d_state, const float* d_proj, int ldp, int z_off, int x_off, int g_off, const float* d_bz,
+              const float* d_bx, const int32_t* d_qo_indptr, const int32_t* d_pos, const int32_t* d_slots, int B, int width,
+              int single_rows, int multi_rows, int out_dtype, void* stream);
+int vb_mingru_tiled(void* d_out, float* d_state, float* d_scratch, const float* d_proj, int ldp, int z_off, int x_off,
+                    int g_off, const float* d_bz, const float* d_bx, const int32_t* d_qo_indptr, const int32_t* d_pos,
+                    const int32_t* d_slots, const int32_t* d_tile_req, const int32_t* d_tile_row0, int n_tiles, int tile_rows,
+                    int B, int width, int out_dtype, void* stream);
 /* Linear attention with a scalar decay per head; q, k, v = silu of the projection columns; state fp32
  * [slots][H][dim][vdim], zero for a request whose first new token has position 0.  single_rows / multi_rows select
  * the step kernel (requests bringing one token) and the chunked kernel (requests bringing more). */

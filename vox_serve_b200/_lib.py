@@ -103,7 +103,8 @@ SIGNATURES = {
     "vb_codec_rmsnorm": (c_int, [P, P, P, c_int, c_int, c_int, c_float, P]),
     "vb_codec_attn_chunk": (c_int, [P, P, P, c_int64, P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, P]),
     "vb_orpheus_window_codes": (c_int, [P, P, P, P, c_int, c_int, P]),
-    "vb_embed_rows_f32": (c_int, [P, P, P, c_int, c_int, c_int, c_int, P, P, c_int, P]),
+    "vb_embed_rows_f32": (c_int, [P, P, P, c_int, c_int, c_int, c_int, P, P, c_int, c_float, P, P]),
+    "vb_gated_residual_norm_f32": (c_int, [P, P, P, c_int, P, P, P, P, c_int, c_int, c_float, c_int, P]),
     "vb_rmsnorm2_f32": (c_int, [P, P, P, P, P, P, c_int, c_int, c_float, c_int, P]),
     "vb_residual_side_f32": (c_int, [P, P, P, c_float, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P, P, P, c_int,
                                      c_int, c_float, c_int, P]),
@@ -116,17 +117,26 @@ SIGNATURES = {
     "vb_layernorm_f32": (c_int, [P, P, P, P, P, c_int, c_int, c_float, c_int, P]),
     "vb_postnorm_residual_f32": (c_int, [P, P, c_int, P, P, P, P, P, c_int, c_int, c_float, c_int, P]),
     "vb_linear": (c_int, [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, P, P, c_int,
-                          C.c_longlong, P]),
+                          C.c_longlong, c_float, c_float, P]),
     "vb_cast_f32_bf16": (c_int, [P, P, C.c_longlong, P]),
     "vb_sum_planes_f32": (c_int, [P, P, c_int, C.c_longlong, P]),
-    "vb_rotary_table": (c_int, [P, P, P, c_int, c_int, P]),
+    "vb_rotary_table": (c_int, [P, P, P, c_int, c_int, C.c_double, P]),
+    "vb_qkv_norm_rotary_append": (c_int, [P, c_int, c_int, c_int, c_int, P, c_int, c_int, P, P, c_float, P, P, P, P, P, P, P,
+                                          c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P]),
+    "vb_latent_rope_append": (c_int, [P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P, c_int, c_int, P, P, P, P, P, P,
+                                      P, c_int, c_int, c_float, c_int, P]),
+    "vb_head_pair_combine": (c_int, [P, P, P, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_int, P]),
+    "vb_mingru": (c_int, [P, P, P, c_int, c_int, c_int, c_int, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P]),
+    "vb_mingru_tiled": (c_int, [P, P, P, P, c_int, c_int, c_int, c_int, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int,
+                                c_int, P]),
+    "vb_gemm_bf16_glu": (c_int, [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, P]),
     "vb_qkv_rotary_append": (c_int, [P, c_int, c_int, c_int, c_int, P, c_int, P, P, P, P, P, P, P, c_int, c_int, c_int,
                                      c_int, c_int, c_int, c_int, P, P, c_int, P]),
     "vb_window_attn": (c_int, [P, P, P, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                               c_int, P, C.c_longlong, P, c_int, P]),
+                               c_int, P, C.c_longlong, P, c_int, c_int, c_int, c_int, c_int, c_int, P]),
     "vb_window_attn_tile_rows": (c_int, []),
     "vb_window_attn_tiled": (c_int, [P, P, P, P, P, c_int, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
-                                     c_int, c_int, c_float, c_int, P]),
+                                     c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_int, c_int, P]),
     "vb_decay_attn": (c_int, [P, P, P, c_int, c_int, c_int, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
                               P]),
     "vb_decay_attn_tile_rows": (c_int, [c_int, c_int]),
@@ -201,7 +211,7 @@ def check(rc: int, what: str = ""):
 # kernels (+ memset nodes) each entry point enqueues; everything not listed launches exactly one
 LAUNCHES = {"vb_set_pdl": 0, "vb_set_trace": 0, "vb_weight_tiles_bytes": 0, "vb_tensor_map_kv": 0,
             "vb_tensor_map_2d_bf16": 0, "vb_device_info": 0, "vb_sample": 1, "vb_update_repetition_cache": 1,
-            "vb_set_gemm_smem_kb": 0, "vb_window_attn_tile_rows": 0, "vb_decay_attn_tile_rows": 0, "vb_decay_attn_tiled": 3, "vb_window_attn": 2}
+            "vb_set_gemm_smem_kb": 0, "vb_window_attn_tile_rows": 0, "vb_decay_attn_tile_rows": 0, "vb_decay_attn_tiled": 3, "vb_window_attn": 2, "vb_mingru_tiled": 3}
 launch_counter = [0]
 
 

@@ -21,11 +21,11 @@ LIB = os.path.join(LIBDIR, "libvoxb200.so")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
 SOURCES = ["api.cu", "elementwise.cu", "attn.cu", "prefill_attn.cu", "prefill_attn_tc.cu", "kvcopy.cu", "encoder.cu", "gemm.cu", "sampler.cu", "snac.cu", "snac_mma.cu",
-           "multicodebook.cu", "mimi.cu", "codec.cu", "norm_linear.cu", "window_attn.cu", "linear_attn.cu", "moe.cu"]
+           "multicodebook.cu", "mimi.cu", "codec.cu", "norm_linear.cu", "window_attn.cu", "linear_attn.cu", "gated_recurrence.cu", "moe.cu"]
 # subsets of the sources that serve one family of models: a first run that only needs that family compiles only these
 # (into lib/libvoxb200_<profile>.so; entry points of the other sources are absent from it)
 PROFILES = {"text": ["api.cu", "elementwise.cu", "gemm.cu", "sampler.cu", "norm_linear.cu", "window_attn.cu", "linear_attn.cu",
-                     "moe.cu"]}
+                     "gated_recurrence.cu", "moe.cu"]}
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC",

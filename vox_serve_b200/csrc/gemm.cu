@@ -65,6 +65,9 @@ struct GemmParams {
   // activation (GemmAct) on the fp32 value
   const __nv_bfloat16* bias;
   int act;
+  // mode 2 with glu_limit > 0: the clamped form g' = min(gate, limit), u' = clamp(up, -limit, limit),
+  // y = g' * sigmoid(glu_slope * g') * (u' + 1), evaluated in fp32 and rounded once
+  float glu_limit, glu_slope;
   // grouped weights (mixture of experts): token tile t_blk multiplies the weights of group tile_group[t_blk] (nullptr:
   // group 0).  A group's matrix starts group_bytes after the previous one (matrices stacked along N), and / or its k-blocks
   // start group_kb after the previous one's inside rows of w_kb_stride k-blocks (matrices stacked along K; 0: the
@@ -356,10 +359,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2) gemm_bf16_kernel(const GemmPa
           const float mine = __uint_as_float(v[2 * i + (hi ? 1 : 0)]);
           const float send = __uint_as_float(v[2 * i + (hi ? 0 : 1)]);       // what the partner lane needs from here
           const float other = __shfl_xor_sync(0xffffffffu, send, 16);
-          const float g = round_bf16(hi ? other : mine);
-          const float up = round_bf16(hi ? mine : other);
-          const float s = round_bf16(g / (1.0f + expf(-g)));
-          o[i] = s * up;
+          if (p.glu_limit > 0.f) {
+            const float g = fminf(hi ? other : mine, p.glu_limit);
+            const float up = fminf(fmaxf(hi ? mine : other, -p.glu_limit), p.glu_limit);
+            o[i] = g / (1.0f + expf(-p.glu_slope * g)) * (up + 1.0f);
+          } else {
+            const float g = round_bf16(hi ? other : mine);
+            const float up = round_bf16(hi ? mine : other);
+            const float s = round_bf16(g / (1.0f + expf(-g)));
+            o[i] = s * up;
+          }
         }
         if (live) {
 #pragma unroll
@@ -728,6 +737,20 @@ int vb_gemm_bf16(void* d_y, const void* d_w_tiles, const void* x_map, const void
   p.bias = static_cast<const __nv_bfloat16*>(d_bias);
   p.act = act;
   return launch_gemm(p, d_w_tiles, x_map, static_cast<cudaStream_t>(stream), d_x_tiles);
+}
+
+int vb_gemm_bf16_glu(void* d_y, const void* d_w_tiles, const void* x_map, int T, int N, int K, int ldy, int tile_rows,
+                     int n_out, float limit, float slope, void* stream) {
+  VB_CHECK_ARG(d_y && d_w_tiles && x_map, "vb_gemm_bf16_glu: null pointer");
+  VB_CHECK_ARG(tile_rows % 32 == 0 && N % tile_rows == 0 && limit > 0.f,
+               "vb_gemm_bf16_glu: needs tile_rows %% 32 == 0, N %% tile_rows == 0 and a positive limit");
+  GemmParams p = {};
+  p.y = d_y; p.T = T; p.N = N; p.K = K; p.ldy = ldy; p.mode = GM_SILU; p.split_k = 1;
+  p.tile_rows = tile_rows;
+  p.n_out = n_out > 0 ? n_out : N / 2;
+  p.t_tile = vb_gemm_t_tile(T);
+  p.glu_limit = limit; p.glu_slope = slope;
+  return launch_gemm(p, d_w_tiles, x_map, static_cast<cudaStream_t>(stream), nullptr);
 }
 
 int vb_gemm_bf16_grouped(void* d_y, const void* d_w_tiles, const void* x_map, int T, int N, int K, int ldy, int mode,

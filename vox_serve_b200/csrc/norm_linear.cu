@@ -33,11 +33,12 @@ __device__ __forceinline__ float block_sum(float v, float* red, int& phase) {
   return warp_sum(t);
 }
 
-// out[t] = table[ids[t]] (+ pos_table[pos[t]]: learned absolute positions, added unscaled in fp32)
+// out[t] = table[ids[t]] * scale (+ pos_table[pos[t]]: learned absolute positions, added unscaled in fp32); out2: a second
+// copy of the rows (stacks that add the embedding again later keep it)
 template <typename WT>
 __global__ void embed_rows_kernel(float* __restrict__ out, const WT* __restrict__ table, const int32_t* __restrict__ ids,
                                   int W, int vocab, const WT* __restrict__ pos_table, const int32_t* __restrict__ pos,
-                                  int n_pos) {
+                                  int n_pos, float scale, float* __restrict__ out2) {
   pdl_sync();
   const int t = blockIdx.x;
   int id = ids[t];
@@ -45,8 +46,42 @@ __global__ void embed_rows_kernel(float* __restrict__ out, const WT* __restrict_
   const WT* src = table + static_cast<size_t>(id) * W;
   const WT* ps = nullptr;
   if (pos_table) ps = pos_table + static_cast<size_t>(min(max(pos[t], 0), n_pos - 1)) * W;
-  for (int i = threadIdx.x; i < W; i += blockDim.x)
-    out[static_cast<size_t>(t) * W + i] = to_f(src[i]) + (ps ? to_f(ps[i]) : 0.f);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = to_f(src[i]) * scale + (ps ? to_f(ps[i]) : 0.f);
+    out[static_cast<size_t>(t) * W + i] = v;
+    if (out2) out2[static_cast<size_t>(t) * W + i] = v;
+  }
+}
+
+// The tail of a pre-norm sublayer with a gated residual, in place on the fp32 row:
+//   x[t] += sigmoid(r[t] + b) * y[t]      (r: the gate's projection of the sublayer's input, b its bias; r == nullptr: x += y)
+//   x[t] += add[t]                        (optional: e.g. the embedding entering a repeated pass over the layers)
+//   out[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w      (optional: what the next sublayer reads)
+template <typename OT>
+__global__ void __launch_bounds__(256) gated_residual_norm_kernel(float* __restrict__ x, const float* __restrict__ y,
+                                                                  const float* __restrict__ r, int ld_r,
+                                                                  const float* __restrict__ bias, const float* __restrict__ add,
+                                                                  OT* __restrict__ out, const float* __restrict__ w, int W,
+                                                                  float eps) {
+  extern __shared__ float sm[];
+  float* row = sm;
+  float* red = sm + W;
+  int phase = 0;
+  pdl_sync();
+  const size_t t = blockIdx.x;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float g = 1.f;
+    if (r) g = 1.f / (1.f + expf(-(r[t * ld_r + i] + (bias ? bias[i] : 0.f))));
+    float v = x[t * W + i] + g * y[t * W + i];
+    if (add) v += add[t * W + i];
+    x[t * W + i] = v;
+    row[i] = v;
+    q = fmaf(v, v, q);
+  }
+  if (out == nullptr) return;
+  const float rs = 1.f / sqrtf(block_sum(q, red, phase) / W + eps);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) out[t * W + i] = from_f<OT>(row[i] * rs * w[i]);
 }
 
 // RMS norm of a row with one or two weights: out1[t] = x[r] / sqrt(mean(x[r]^2) + eps) * w1, out2[t] likewise with w2
@@ -436,6 +471,9 @@ struct LinearParams {
   long long x_group_stride, o_group_stride;     // batched form (both 0 otherwise)
   const float* gate;
   int ld_gate;
+  // epilogue 1 with glu_limit > 0: the clamped form g' = min(gate, limit), u' = clamp(up, -limit, limit),
+  // out = g' * sigmoid(glu_slope * g') * (u' + 1)
+  float glu_limit, glu_slope;
 };
 
 template <typename XT, typename WT, typename OT, int EPI>
@@ -508,8 +546,14 @@ __global__ void __launch_bounds__(256) linear_kernel(LinearParams p) {
       if (n >= p.N) continue;
       float v;
       if (EPI == 1) {
-        const float g = acc[0][i][j], u = acc[NB - 1][i][j];
-        v = g / (1.f + expf(-g)) * u;
+        float g = acc[0][i][j], u = acc[NB - 1][i][j];
+        if (p.glu_limit > 0.f) {
+          g = fminf(g, p.glu_limit);
+          u = fminf(fmaxf(u, -p.glu_limit), p.glu_limit);
+          v = g / (1.f + expf(-p.glu_slope * g)) * (u + 1.f);
+        } else {
+          v = g / (1.f + expf(-g)) * u;
+        }
       } else {
         v = act_apply(acc[0][i][j] * p.alpha, p.epi) * gmul;
       }
@@ -623,12 +667,29 @@ using bf16 = __nv_bfloat16;
 extern "C" {
 
 int vb_embed_rows_f32(float* d_out, const void* d_table, const int32_t* d_ids, int T, int width, int vocab, int dtype,
-                      const void* d_pos_table, const int32_t* d_pos, int n_pos, void* stream) {
+                      const void* d_pos_table, const int32_t* d_pos, int n_pos, float scale, float* d_out2, void* stream) {
   VB_CHECK_ARG(d_out && d_table && d_ids && width > 0 && vocab > 0, "vb_embed_rows_f32: bad arguments");
   VB_CHECK_ARG(!d_pos_table || (d_pos && n_pos > 0), "vb_embed_rows_f32: a position table needs positions");
   if (T <= 0) return 0;
-  if (dtype == 1) VB_LAUNCH_PDL(embed_rows_kernel<float>, T, 128, 0, stream, d_out, static_cast<const float*>(d_table), d_ids, width, vocab, static_cast<const float*>(d_pos_table), d_pos, n_pos);
-  else VB_LAUNCH_PDL(embed_rows_kernel<bf16>, T, 128, 0, stream, d_out, static_cast<const bf16*>(d_table), d_ids, width, vocab, static_cast<const bf16*>(d_pos_table), d_pos, n_pos);
+  if (dtype == 1) VB_LAUNCH_PDL(embed_rows_kernel<float>, T, 128, 0, stream, d_out, static_cast<const float*>(d_table), d_ids, width, vocab, static_cast<const float*>(d_pos_table), d_pos, n_pos, scale, d_out2);
+  else VB_LAUNCH_PDL(embed_rows_kernel<bf16>, T, 128, 0, stream, d_out, static_cast<const bf16*>(d_table), d_ids, width, vocab, static_cast<const bf16*>(d_pos_table), d_pos, n_pos, scale, d_out2);
+  return 0;
+}
+
+int vb_gated_residual_norm_f32(float* d_x, const float* d_y, const float* d_r, int ld_r, const float* d_bias,
+                               const float* d_add, void* d_out, const float* d_w, int T, int width, float eps, int out_dtype,
+                               void* stream) {
+  VB_CHECK_ARG(d_x && d_y && width > 0 && (!d_out || d_w) && (!d_r || ld_r >= width), "vb_gated_residual_norm_f32: bad arguments");
+  if (T <= 0) return 0;
+  const size_t smem = (static_cast<size_t>(width) + 64) * sizeof(float);
+  VB_CHECK_ARG(smem <= static_cast<size_t>(VB_MAX_DYN_SMEM), "vb_gated_residual_norm_f32: width %d too large", width);
+  if (out_dtype == 1) {
+    if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(gated_residual_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+    VB_LAUNCH_PDL(gated_residual_norm_kernel<float>, T, 256, smem, stream, d_x, d_y, d_r, ld_r, d_bias, d_add, static_cast<float*>(d_out), d_w, width, eps);
+  } else {
+    if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(gated_residual_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+    VB_LAUNCH_PDL(gated_residual_norm_kernel<bf16>, T, 256, smem, stream, d_x, d_y, d_r, ld_r, d_bias, d_add, static_cast<bf16*>(d_out), d_w, width, eps);
+  }
   return 0;
 }
 
@@ -756,12 +817,13 @@ int vb_postnorm_residual_f32(float* d_x, const float* d_y, int y_planes, const f
 
 int vb_linear(void* d_out, const void* d_x, const void* d_w, int T, int N, int K, int ldx, int ldo, int in_dtype,
               int out_dtype, int epilogue, float alpha, const int32_t* d_row_off, const int32_t* d_gather, int groups,
-              long long w_group_stride, void* stream) {
+              long long w_group_stride, float glu_limit, float glu_slope, void* stream) {
   VB_CHECK_ARG(d_out && d_x && d_w && N > 0 && K > 0 && ldx >= K && ldo >= N, "vb_linear: bad arguments");
   VB_CHECK_ARG(epilogue >= 0 && epilogue <= 4, "vb_linear: epilogue %d", epilogue);
   VB_CHECK_ARG(groups >= 1 && (groups == 1 || d_row_off), "vb_linear: grouped launches need row offsets");
   if (T <= 0) return 0;
-  LinearParams p{d_out, d_x, d_w, d_row_off, d_gather, T, N, K, ldx, ldo, epilogue, w_group_stride, alpha, 0, 0, nullptr, 0};
+  LinearParams p{d_out, d_x, d_w, d_row_off, d_gather, T, N, K, ldx, ldo, epilogue, w_group_stride, alpha, 0, 0, nullptr, 0,
+                 glu_limit, glu_slope};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // in_dtype: 0 = bf16 activations and weights, 1 = fp32 both; out_dtype likewise
   if (in_dtype == 1) return out_dtype == 1 ? launch_linear<float, float, float>(p, groups, T, s) : launch_linear<float, float, bf16>(p, groups, T, s);

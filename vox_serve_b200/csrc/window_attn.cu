@@ -27,15 +27,15 @@ template <> __device__ __forceinline__ float wa_from_f<float>(float v) { return 
 template <> __device__ __forceinline__ __nv_bfloat16 wa_from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
 __global__ void rotary_table_kernel(float* __restrict__ cs, const int32_t* __restrict__ pos, const double* __restrict__ freq,
-                                    int T, int half) {
+                                    int T, int half, double mult) {
   pdl_sync();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= T * half) return;
   const int t = i / half, j = i - t * half;
   double s, c;
   sincos(static_cast<double>(pos[t]) * freq[j], &s, &c);
-  cs[(static_cast<size_t>(t) * 2) * half + j] = static_cast<float>(c);
-  cs[(static_cast<size_t>(t) * 2 + 1) * half + j] = static_cast<float>(s);
+  cs[(static_cast<size_t>(t) * 2) * half + j] = static_cast<float>(c * mult);
+  cs[(static_cast<size_t>(t) * 2 + 1) * half + j] = static_cast<float>(s * mult);
 }
 
 struct QkvTailParams {
@@ -147,6 +147,155 @@ __global__ void __launch_bounds__(128) latent_norm_append_kernel(LatentTailParam
   for (int i = threadIdx.x; i < p.kv_rank; i += 128) co[i] = wa_from_f<CT>(c[i] * rc * p.wc[i]);
 }
 
+// The tail of a fused q|k|v|.. projection for heads that are normed before they are rotated: every query and key head
+// (for attention with several score maps per head, every map is a head here) is RMS-normed over its dim values with a
+// weight shared by all heads (optional), then its first 2 * half dims are rotated -- pairs (2i, 2i + 1) in the
+// interleaved layout, pairs (i, i + half) in the half layout -- and written out / appended; values are appended as they are.
+// The key cache holds Gk heads per token, the value cache Gv (Gk / Gv key heads read one value head).  One warp per head.
+struct QkvNormTailParams {
+  const float* proj;      // [T][ldp]
+  int ldp, q_off, k_off, v_off;
+  const float* cs;        // [T][2][half] or nullptr
+  int half, layout;       // layout 0: interleaved pairs, 1: halves
+  const float* q_norm;    // [dim] or nullptr
+  const float* k_norm;
+  float eps;
+  void* q_out;            // [T][Hq * dim]
+  void* k_cache;          // [pages][page][Gk][dim]
+  void* v_cache;          // [pages][page][Gv][vdim]
+  const int32_t* row_req;
+  const int32_t* pos;
+  const int32_t* page_indptr;
+  const int32_t* page_indices;
+  int page_size, Hq, Gk, Gv, dim, vdim;
+};
+
+__device__ __forceinline__ float rotated_value(const float* __restrict__ src, const float* __restrict__ w, float r,
+                                               const float* __restrict__ cs, int half, int layout, int d) {
+  // value d of a head after norm (scale r, weight w) and rotation
+  const float x = src[d] * r * (w ? w[d] : 1.f);
+  if (cs == nullptr || d >= 2 * half) return x;
+  int i, partner;
+  bool first;
+  if (layout == 0) { i = d >> 1; first = (d & 1) == 0; partner = d ^ 1; }
+  else { first = d < half; i = first ? d : d - half; partner = first ? d + half : d - half; }
+  const float y = src[partner] * r * (w ? w[partner] : 1.f);
+  const float c = cs[i], sn = cs[half + i];
+  return first ? x * c - y * sn : x * c + y * sn;
+}
+
+template <typename CT>
+__global__ void __launch_bounds__(256) qkv_norm_rotary_append_kernel(QkvNormTailParams p) {
+  pdl_sync();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float* row = p.proj + static_cast<size_t>(t) * p.ldp;
+  const int b = p.row_req[t], ps = p.pos[t];
+  const size_t tok = static_cast<size_t>(p.page_indices[p.page_indptr[b] + ps / p.page_size]) * p.page_size + ps % p.page_size;
+  const float* cs = p.cs ? p.cs + static_cast<size_t>(t) * 2 * p.half : nullptr;
+  CT* q_out = static_cast<CT*>(p.q_out) + static_cast<size_t>(t) * p.Hq * p.dim;
+  CT* k_out = static_cast<CT*>(p.k_cache) + tok * p.Gk * p.dim;
+  CT* v_out = static_cast<CT*>(p.v_cache) + tok * p.Gv * p.vdim;
+  for (int hh = warp; hh < p.Hq + p.Gk; hh += 8) {
+    const bool is_q = hh < p.Hq;
+    const int h = is_q ? hh : hh - p.Hq;
+    const float* src = row + (is_q ? p.q_off : p.k_off) + h * p.dim;
+    const float* w = is_q ? p.q_norm : p.k_norm;
+    float r = 1.f;
+    if (w) {
+      float ss = 0.f;
+      for (int d = lane; d < p.dim; d += 32) ss = fmaf(src[d], src[d], ss);
+      r = 1.f / sqrtf(warp_sum(ss) / p.dim + p.eps);
+    }
+    CT* dst = (is_q ? q_out : k_out) + h * p.dim;
+    for (int d = lane; d < p.dim; d += 32) dst[d] = wa_from_f<CT>(rotated_value(src, w, r, cs, p.half, p.layout, d));
+  }
+  for (int i = threadIdx.x; i < p.Gv * p.vdim; i += 256) v_out[i] = wa_from_f<CT>(row[p.v_off + i]);
+}
+
+// The tail of a fused (queries | key/value latent + shared rotated key part | ...) projection of latent attention whose
+// heads have an unrotated part of `dim` and a rotated part of `rot` dims: the latent (kv_rank dims) is RMS-normed with its
+// weight, the shared key part is rotated, and both are appended to the layer's pages as ONE row [kv_rank | rot] per token.
+// The queries' unrotated parts go to q_out [T][H][dim] (they are carried into latent space by a per-head projection), their
+// rotated parts straight to their place behind the latent-space part: q_lat[t][h][kv_rank .. kv_rank + rot).
+struct LatentRopeTailParams {
+  const float* proj;      // [T][ldp]
+  int ldp, q_off, c_off, H, dim, rot, kv_rank;
+  const float* wc;        // [kv_rank]
+  const float* cs;        // [T][2][half] or nullptr
+  int half, layout;
+  void* q_out;            // [T][H][dim]
+  void* q_lat;            // [T][H][kv_rank + rot]
+  void* cache;            // [pages][page][kv_rank + rot]
+  const int32_t* row_req;
+  const int32_t* pos;
+  const int32_t* page_indptr;
+  const int32_t* page_indices;
+  int page_size;
+  float eps;
+};
+
+template <typename CT>
+__global__ void __launch_bounds__(128) latent_rope_append_kernel(LatentRopeTailParams p) {
+  __shared__ float red[4];
+  pdl_sync();
+  const size_t t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float* row = p.proj + t * p.ldp;
+  const float* c = row + p.c_off;
+  const float* cs = p.cs ? p.cs + t * 2 * p.half : nullptr;
+  float sc = 0.f;
+  for (int i = threadIdx.x; i < p.kv_rank; i += 128) sc = fmaf(c[i], c[i], sc);
+  sc = warp_sum(sc);
+  if (lane == 0) red[warp] = sc;
+  __syncthreads();
+  sc = red[0] + red[1] + red[2] + red[3];
+  const float rc = 1.f / sqrtf(sc / p.kv_rank + p.eps);
+  const int b = p.row_req[t], ps = p.pos[t];
+  const size_t tok = static_cast<size_t>(p.page_indices[p.page_indptr[b] + ps / p.page_size]) * p.page_size + ps % p.page_size;
+  const int ldc = p.kv_rank + p.rot;
+  CT* co = static_cast<CT*>(p.cache) + tok * ldc;
+  for (int i = threadIdx.x; i < p.kv_rank; i += 128) co[i] = wa_from_f<CT>(c[i] * rc * p.wc[i]);
+  for (int i = threadIdx.x; i < p.rot; i += 128)
+    co[p.kv_rank + i] = wa_from_f<CT>(rotated_value(c + p.kv_rank, nullptr, 1.f, cs, p.half, p.layout, i));
+  const int dq = p.dim + p.rot;
+  CT* qo = static_cast<CT*>(p.q_out) + t * p.H * p.dim;
+  CT* ql = static_cast<CT*>(p.q_lat) + t * p.H * ldc;
+  for (int i = threadIdx.x; i < p.H * dq; i += 128) {
+    const int h = i / dq, d = i - h * dq;
+    const float* src = row + p.q_off + h * dq;
+    if (d < p.dim) qo[h * p.dim + d] = wa_from_f<CT>(src[d]);
+    else ql[h * ldc + p.kv_rank + d - p.dim] = wa_from_f<CT>(rotated_value(src + p.dim, nullptr, 1.f, cs, p.half, p.layout, d - p.dim));
+  }
+}
+
+// Attention with two score maps per head over the same values: the maps' outputs a1, a2 (fp32 [T][2H][vdim], laid out per
+// key/value group as [map 1 of the group's R heads | map 2 of them]) are combined as o = a1 - lambda * a2, o is divided by
+// its root mean square over the head's vdim values, times `post`, times sigmoid(gate).  One warp per (token, head).
+template <typename CT>
+__global__ void __launch_bounds__(128) head_pair_combine_kernel(CT* __restrict__ out, const float* __restrict__ a,
+                                                                const float* __restrict__ gate, int ld_gate, int T, int H,
+                                                                int R, int vdim, float lambda, float post, float eps) {
+  pdl_sync();
+  const int idx = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (idx >= T * H) return;
+  const int t = idx / H, h = idx - t * H, g = h / R, j = h - g * R;
+  const float* a1 = a + (static_cast<size_t>(t) * 2 * H + g * 2 * R + j) * vdim;
+  const float* a2 = a1 + static_cast<size_t>(R) * vdim;
+  float ss = 0.f;
+  for (int d = lane; d < vdim; d += 32) {
+    const float o = a1[d] - lambda * a2[d];
+    ss = fmaf(o, o, ss);
+  }
+  const float r = post / sqrtf(warp_sum(ss) / vdim + eps);
+  const float* gt = gate ? gate + static_cast<size_t>(t) * ld_gate + h * vdim : nullptr;
+  CT* o_row = out + (static_cast<size_t>(t) * H + h) * vdim;
+  for (int d = lane; d < vdim; d += 32) {
+    float o = (a1[d] - lambda * a2[d]) * r;
+    if (gt) o *= 1.f / (1.f + expf(-gt[d]));
+    o_row[d] = wa_from_f<CT>(o);
+  }
+}
+
 struct WindowAttnParams {
   const void* q;          // [T][H][dim]
   const void* k_cache;
@@ -162,6 +311,12 @@ struct WindowAttnParams {
   const int32_t* tile_req;    // tiled kernel: request of tile i
   const int32_t* tile_row0;   // tiled kernel: first row of tile i
   int T, H, G, dim, vdim, page_size, window;   // window <= 0: every earlier position is visible
+  int chunk;                  // > 0: a position sees only the keys of its own block of `chunk` positions (blocks counted from
+                              // position 0 of the sequence)
+  int k_ld, v_ld;             // elements per token of the key / value cache (G * dim, (G / v_share) * vdim for caches of their own;
+                              // a value that is a leading slice of the key row has v_ld = k_ld)
+  int v_share;                // consecutive key heads that read ONE value head (1: every key head has its own)
+  int out_f32;                // the output is fp32 whatever the operand type (it feeds a combination of heads done in fp32)
   float scale;
   const int32_t* row_list;    // per-row kernels: the rows to serve (nullptr: rows 0 .. T - 1); T counts the served rows
   int row_heads;              // tensor-core tile kernel on single-token rows: a tile's rows are the query heads of ONE token
@@ -169,6 +324,18 @@ struct WindowAttnParams {
   int splits;                 // grouped kernel: key tiles are dealt round-robin to `splits` CTAs per (row, key/value head)
   float* part;                // [T][H][splits][vdim + 2]: unnormalised output, running max, running sum of every split
 };
+
+// first visible key of a query at position pos: the sliding window's start, the start of the position's chunk, or 0
+__device__ __forceinline__ int wa_first_key(const WindowAttnParams& p, int pos) {
+  int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  if (p.chunk > 0) lo = max(lo, pos - pos % p.chunk);
+  return lo;
+}
+template <typename CT>
+__device__ __forceinline__ void wa_store(const WindowAttnParams& p, size_t idx, float v) {
+  if (p.out_f32) static_cast<float*>(p.out)[idx] = v;
+  else static_cast<CT*>(p.out)[idx] = wa_from_f<CT>(v);
+}
 
 template <typename CT>
 __device__ __forceinline__ float dot_row(const float* __restrict__ q, const CT* __restrict__ k, int dim);
@@ -207,10 +374,11 @@ __device__ __forceinline__ float dot_row<__nv_bfloat16>(const float* __restrict_
 // are zero.  16-byte loads when the head size allows (8 bf16 / 4 fp32 per load), element loads otherwise.
 template <typename CT>
 __device__ __forceinline__ void load_rows_f32(float* __restrict__ dst, int ldd, const CT* __restrict__ cache,
-                                              const int32_t* __restrict__ pages, int page_size, int G, int g, int d_head,
+                                              const int32_t* __restrict__ pages, int page_size, int ld, int off, int d_head,
                                               int c0, int n_rows, int valid, int tid, int nthreads) {
+  // the head's d_head values of token tok start at cache[tok * ld + off]
   constexpr int VEC = 16 / sizeof(CT);
-  if (d_head % VEC == 0) {
+  if (d_head % VEC == 0 && ld % VEC == 0 && off % VEC == 0) {
     const int nvec = d_head / VEC;
     for (int i = tid; i < n_rows * nvec; i += nthreads) {
       const int kk = i / nvec, d = (i - kk * nvec) * VEC;
@@ -218,7 +386,7 @@ __device__ __forceinline__ void load_rows_f32(float* __restrict__ dst, int ldd, 
       if (kk < valid) {
         const int kj = c0 + kk;
         const size_t tok = static_cast<size_t>(pages[kj / page_size]) * page_size + kj % page_size;
-        const uint4 v = *reinterpret_cast<const uint4*>(cache + (tok * G + g) * d_head + d);
+        const uint4 v = *reinterpret_cast<const uint4*>(cache + tok * ld + off + d);
         if constexpr (sizeof(CT) == 2) {
           o[0] = bf16_lo(v.x); o[1] = bf16_hi(v.x); o[2] = bf16_lo(v.y); o[3] = bf16_hi(v.y);
           o[4] = bf16_lo(v.z); o[5] = bf16_hi(v.z); o[6] = bf16_lo(v.w); o[7] = bf16_hi(v.w);
@@ -237,7 +405,7 @@ __device__ __forceinline__ void load_rows_f32(float* __restrict__ dst, int ldd, 
       if (kk < valid) {
         const int kj = c0 + kk;
         const size_t tok = static_cast<size_t>(pages[kj / page_size]) * page_size + kj % page_size;
-        v = wa_to_f(cache[(tok * G + g) * d_head + d]);
+        v = wa_to_f(cache[tok * ld + off + d]);
       }
       dst[kk * ldd + d] = v;
     }
@@ -260,7 +428,8 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attn_kernel(WindowAttnPa
   __syncwarp();
   const int b = p.row_req[t], ps = p.pos[t], g = h / (p.H / p.G);
   const int32_t* pages = p.page_indices + p.page_indptr[b];
-  const int lo = p.window > 0 ? max(0, ps - p.window + 1) : 0;
+  const int lo = wa_first_key(p, ps);
+  const int gv = g / p.v_share;
   const CT* kc = static_cast<const CT*>(p.k_cache);
   const CT* vc = static_cast<const CT*>(p.v_cache);
   float m = -INFINITY, l = 0.f, acc[WA_MAXU];
@@ -273,7 +442,7 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attn_kernel(WindowAttnPa
     float s = -INFINITY;
     if (ok) {
       tok = pages[kj / p.page_size] * p.page_size + kj % p.page_size;
-      s = dot_row<CT>(qs, kc + (static_cast<size_t>(tok) * p.G + g) * p.dim, p.dim);
+      s = dot_row<CT>(qs, kc + static_cast<size_t>(tok) * p.k_ld + g * p.dim, p.dim);
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float corr = expf(m - m_new);          // m = -inf on the first chunk: exp(-inf) = 0
@@ -286,7 +455,7 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attn_kernel(WindowAttnPa
     for (int jj = 0; jj < n; ++jj) {
       const float pv = __shfl_sync(0xffffffffu, pj, jj);
       const int tk = __shfl_sync(0xffffffffu, tok, jj);
-      const CT* vr = vc + (static_cast<size_t>(tk) * p.G + g) * p.vdim;
+      const CT* vr = vc + static_cast<size_t>(tk) * p.v_ld + gv * p.vdim;
 #pragma unroll
       for (int u = 0; u < WA_MAXU; ++u) {
         const int d = lane + 32 * u;
@@ -295,7 +464,7 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attn_kernel(WindowAttnPa
     }
   }
   const float inv = 1.f / l;
-  CT* out = static_cast<CT*>(p.out) + static_cast<size_t>(t) * p.H * p.vdim + h * p.vdim;
+  const size_t out0 = static_cast<size_t>(t) * p.H * p.vdim + h * p.vdim;
   const float* gate = p.gate ? p.gate + static_cast<size_t>(t) * p.ld_gate + h * p.vdim : nullptr;
 #pragma unroll
   for (int u = 0; u < WA_MAXU; ++u) {
@@ -303,7 +472,7 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attn_kernel(WindowAttnPa
     if (d < p.vdim) {
       float o = acc[u] * inv;
       if (gate) o *= 1.f / (1.f + expf(-gate[d]));
-      out[d] = wa_from_f<CT>(o);
+      wa_store<CT>(p, out0 + d, o);
     }
   }
 }
@@ -338,8 +507,9 @@ __global__ void __launch_bounds__(256) window_attn_tiled_kernel(WindowAttnParams
   const int pos0 = p.pos[row0], pos_last = pos0 + nrows - 1;     // rows of a portion are consecutive positions
   const int my_pos = pos0 + r;
   const bool row_ok = r < nrows;
-  const int my_lo = p.window > 0 ? max(0, my_pos - p.window + 1) : 0;
-  const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int my_lo = wa_first_key(p, my_pos);
+  const int lo = wa_first_key(p, pos0);
+  const int gv = g / p.v_share;
   const int32_t* pages = p.page_indices + p.page_indptr[b];
   const CT* kc = static_cast<const CT*>(p.k_cache);
   const CT* vc = static_cast<const CT*>(p.v_cache);
@@ -351,8 +521,8 @@ __global__ void __launch_bounds__(256) window_attn_tiled_kernel(WindowAttnParams
   for (int c0 = lo; c0 <= pos_last; c0 += WT_KEYS) {
     __syncthreads();
     const int valid = min(WT_KEYS, pos_last - c0 + 1);
-    load_rows_f32<CT>(Ks, dkp, kc, pages, p.page_size, p.G, g, dk, c0, WT_KEYS, valid, tid, 256);
-    load_rows_f32<CT>(Vs, dvp, vc, pages, p.page_size, p.G, g, dv, c0, WT_KEYS, valid, tid, 256);
+    load_rows_f32<CT>(Ks, dkp, kc, pages, p.page_size, p.k_ld, g * dk, dk, c0, WT_KEYS, valid, tid, 256);
+    load_rows_f32<CT>(Vs, dvp, vc, pages, p.page_size, p.v_ld, gv * dv, dv, c0, WT_KEYS, valid, tid, 256);
     __syncthreads();
     // scores of this thread's 8 keys
     float s[WT_KEYS / 4];
@@ -401,7 +571,7 @@ __global__ void __launch_bounds__(256) window_attn_tiled_kernel(WindowAttnParams
   if (!row_ok) return;
   const int t = row0 + r;
   const float inv = 1.f / l;
-  CT* out = static_cast<CT*>(p.out) + static_cast<size_t>(t) * p.H * dv + h * dv;
+  const size_t out0 = static_cast<size_t>(t) * p.H * dv + h * dv;
   const float* gate = p.gate ? p.gate + static_cast<size_t>(t) * p.ld_gate + h * dv : nullptr;
 #pragma unroll
   for (int u = 0; u < WT_MAXD; ++u) {
@@ -409,7 +579,7 @@ __global__ void __launch_bounds__(256) window_attn_tiled_kernel(WindowAttnParams
     if (u < nd && d < dv) {
       float o = acc[u] * inv;
       if (gate) o *= 1.f / (1.f + expf(-gate[d]));
-      out[d] = wa_from_f<CT>(o);
+      wa_store<CT>(p, out0 + d, o);
     }
   }
 }
@@ -438,7 +608,8 @@ __global__ void __launch_bounds__(128) window_attn_group_kernel(WindowAttnParams
   for (int i = tid; i < R * dk; i += 128) Qs[i] = wa_to_f(q[i]) * p.scale;
   const int b = p.row_req[t], ps = p.pos[t];
   const int32_t* pages = p.page_indices + p.page_indptr[b];
-  const int lo = p.window > 0 ? max(0, ps - p.window + 1) : 0;
+  const int lo = wa_first_key(p, ps);
+  const int gv = g / p.v_share;
   const CT* kc = static_cast<const CT*>(p.k_cache);
   const CT* vc = static_cast<const CT*>(p.v_cache);
   float m[WD_RU], l[WD_RU], acc[WD_RU][WD_VU];
@@ -453,8 +624,8 @@ __global__ void __launch_bounds__(128) window_attn_group_kernel(WindowAttnParams
   for (int c0 = lo + sidx * WD_KEYS; c0 <= ps; c0 += S * WD_KEYS) {
     __syncthreads();
     const int nk = min(WD_KEYS, ps - c0 + 1);
-    load_rows_f32<CT>(Ks, dkp, kc, pages, p.page_size, p.G, g, dk, c0, WD_KEYS, nk, tid, 128);
-    load_rows_f32<CT>(Vs, dvp, vc, pages, p.page_size, p.G, g, dv, c0, WD_KEYS, nk, tid, 128);
+    load_rows_f32<CT>(Ks, dkp, kc, pages, p.page_size, p.k_ld, g * dk, dk, c0, WD_KEYS, nk, tid, 128);
+    load_rows_f32<CT>(Vs, dvp, vc, pages, p.page_size, p.v_ld, gv * dv, dv, c0, WD_KEYS, nk, tid, 128);
     __syncthreads();
 #pragma unroll
     for (int u = 0; u < WD_RU; ++u) {
@@ -506,7 +677,7 @@ __global__ void __launch_bounds__(128) window_attn_group_kernel(WindowAttnParams
       continue;
     }
     const float inv = 1.f / l[u];
-    CT* out = static_cast<CT*>(p.out) + static_cast<size_t>(t) * p.H * dv + h * dv;
+    const size_t out0 = static_cast<size_t>(t) * p.H * dv + h * dv;
     const float* gate = p.gate ? p.gate + static_cast<size_t>(t) * p.ld_gate + h * dv : nullptr;
 #pragma unroll
     for (int v = 0; v < WD_VU; ++v) {
@@ -514,7 +685,7 @@ __global__ void __launch_bounds__(128) window_attn_group_kernel(WindowAttnParams
       if (d < dv) {
         float o = acc[u][v] * inv;
         if (gate) o *= 1.f / (1.f + expf(-gate[d]));
-        out[d] = wa_from_f<CT>(o);
+        wa_store<CT>(p, out0 + d, o);
       }
     }
   }
@@ -537,13 +708,13 @@ __global__ void __launch_bounds__(64) window_attn_merge_kernel(WindowAttnParams 
     wgt[s] = w / L;
   }
   __syncthreads();
-  CT* out = static_cast<CT*>(p.out) + static_cast<size_t>(t) * p.H * dv + h * dv;
+  const size_t out0 = static_cast<size_t>(t) * p.H * dv + h * dv;
   const float* gate = p.gate ? p.gate + static_cast<size_t>(t) * p.ld_gate + h * dv : nullptr;
   for (int d = threadIdx.x; d < dv; d += blockDim.x) {
     float o = 0.f;
     for (int s = 0; s < S; ++s) o = fmaf(pt[s * (dv + 2) + d], wgt[s], o);
     if (gate) o *= 1.f / (1.f + expf(-gate[d]));
-    out[d] = wa_from_f<CT>(o);
+    wa_store<CT>(p, out0 + d, o);
   }
 }
 
@@ -574,8 +745,9 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnParams p
     HH = p.H; pstep = 1; pos0 = p.pos[row0]; g = h / (p.H / p.G);
   }
   // keys and values that are one tensor of equal head sizes (latent attention) are staged once and read as both
-  const bool same_kv = p.k_cache == p.v_cache && p.dim == p.vdim;
-  const int dk = p.dim, dv = p.vdim, ldk = dk + 8, ldv = dv + 8, nkb = dk / 16, nvp = dv / 16;
+  // (also values that are a leading slice of the one key head: the shared latent with a rotated key part behind it)
+  const bool same_kv = p.k_cache == p.v_cache && p.k_ld == p.v_ld && p.G == 1 && p.v_share == 1 && p.vdim <= p.dim;
+  const int dk = p.dim, dv = p.vdim, ldk = dk + 8, ldv = same_kv ? ldk : dv + 8, nkb = dk / 16, nvp = dv / 16;
   // two stages of K [64][dk + 8] | V [64][dv + 8]; the first stage's K region holds the Q tile first
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smraw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -596,8 +768,9 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnParams p
   const int rA = warp * 16 + (lane >> 2), rB = rA + 8;
   const int posA = pos0 + rA * pstep, posB = pos0 + rB * pstep;
   const bool okA = rA < nrows, okB = rB < nrows;
-  const int loA = p.window > 0 ? max(0, posA - p.window + 1) : 0, loB = p.window > 0 ? max(0, posB - p.window + 1) : 0;
-  const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int loA = wa_first_key(p, posA), loB = wa_first_key(p, posB);
+  const int lo = wa_first_key(p, pos0);
+  const int gv = g / p.v_share;
   const int32_t* pages = p.page_indices + p.page_indptr[b];
   const __nv_bfloat16* kc = static_cast<const __nv_bfloat16*>(p.k_cache);
   const __nv_bfloat16* vc = static_cast<const __nv_bfloat16*>(p.v_cache);
@@ -608,7 +781,7 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnParams p
   const int vv = dv / 8;
   // K / V tiles are double-buffered: the asynchronous copies of tile i + 1 are in flight while tile i is multiplied
   // (cp.async of 16 bytes; rows past the request's last position are filled with zeros by a zero source size)
-  const int stage_elems = FN * (ldk + ldv);
+  const int stage_elems = FN * (ldk + dv + 8);
   // thread t copies 16-byte piece (t % 16) + 16 n of rows (t / 16) + 8 m: the page lookup and the row's cache offset are
   // computed once per row and serve its K and its V pieces
   auto issue_tile = [&](int c0, int stage) {
@@ -621,15 +794,15 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnParams p
       const bool ok = kj <= pos_last;
       const int kq = ok ? kj : pos_last;                 // (a valid address also for the zero-filled rows)
       const int pg = kq / p.page_size;
-      const size_t tok = (static_cast<size_t>(pages[pg]) * p.page_size + (kq - pg * p.page_size)) * p.G + g;
+      const size_t tok = static_cast<size_t>(pages[pg]) * p.page_size + (kq - pg * p.page_size);
       const uint32_t nbytes = ok ? 16u : 0u;
       for (int c = piece; c < qv; c += 16)
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(Kd + kk * ldk + c * 8)),
-                     "l"(kc + tok * dk + c * 8), "r"(nbytes) : "memory");
+                     "l"(kc + tok * p.k_ld + g * dk + c * 8), "r"(nbytes) : "memory");
       if (!same_kv)
         for (int c = piece; c < vv; c += 16)
           asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(Vd + kk * ldv + c * 8)),
-                       "l"(vc + tok * dv + c * 8), "r"(nbytes) : "memory");
+                       "l"(vc + tok * p.v_ld + gv * dv + c * 8), "r"(nbytes) : "memory");
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -649,7 +822,7 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnParams p
     const __nv_bfloat16* Vt = same_kv ? Kt : Kt + FN * ldk;
     // a warp whose 16 rows see nothing of this tile has no work in it
     const int w_first = pos0 + warp * 16 * pstep, w_last = min(pos0 + (warp * 16 + 15) * pstep, pos_last);
-    const int w_lo = p.window > 0 ? max(0, w_first - p.window + 1) : 0;
+    const int w_lo = wa_first_key(p, w_first);
     const bool idle = warp * 16 >= nrows || c0 > w_last || c0 + FN - 1 < w_lo;
     if (!idle) {
     float sc[FN / 8][4];
@@ -764,7 +937,9 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnParams p
           x0 *= 1.f / (1.f + expf(-gt[0]));
           x1 *= 1.f / (1.f + expf(-gt[1]));
         }
-        *reinterpret_cast<uint32_t*>(out + static_cast<size_t>(t) * HH * dv + h * dv + d) = pack_bf16(x0, x1);
+        const size_t oi = static_cast<size_t>(t) * HH * dv + h * dv + d;
+        if (p.out_f32) *reinterpret_cast<float2*>(static_cast<float*>(p.out) + oi) = make_float2(x0, x1);
+        else *reinterpret_cast<uint32_t*>(out + oi) = pack_bf16(x0, x1);
       }
     }
   }
@@ -777,10 +952,61 @@ using bf16 = __nv_bfloat16;
 
 extern "C" {
 
-int vb_rotary_table(float* d_cs, const int32_t* d_pos, const double* d_freq, int T, int half, void* stream) {
+int vb_rotary_table(float* d_cs, const int32_t* d_pos, const double* d_freq, int T, int half, double mult, void* stream) {
   VB_CHECK_ARG(d_cs && d_pos && d_freq && half > 0, "vb_rotary_table: bad arguments");
   if (T <= 0) return 0;
-  VB_LAUNCH_PDL(rotary_table_kernel, (T * half + 255) / 256, 256, 0, stream, d_cs, d_pos, d_freq, T, half);
+  VB_LAUNCH_PDL(rotary_table_kernel, (T * half + 255) / 256, 256, 0, stream, d_cs, d_pos, d_freq, T, half, mult);
+  return 0;
+}
+
+int vb_qkv_norm_rotary_append(const float* d_proj, int ldp, int q_off, int k_off, int v_off, const float* d_cs, int half,
+                              int layout, const float* d_q_norm, const float* d_k_norm, float eps, void* d_q_out,
+                              void* d_k_cache, void* d_v_cache, const int32_t* d_row_req, const int32_t* d_pos,
+                              const int32_t* d_page_indptr, const int32_t* d_page_indices, int page_size, int T, int Hq, int Gk,
+                              int Gv, int dim, int vdim, int dtype, void* stream) {
+  VB_CHECK_ARG(d_proj && d_q_out && d_k_cache && d_v_cache && d_row_req && d_pos && d_page_indptr && d_page_indices,
+               "vb_qkv_norm_rotary_append: null pointer");
+  VB_CHECK_ARG(Hq > 0 && Gk > 0 && Gv > 0 && dim > 0 && vdim > 0 && page_size > 0 && half >= 0 && 2 * half <= dim &&
+               (layout == 0 || layout == 1), "vb_qkv_norm_rotary_append: bad sizes Hq=%d Gk=%d Gv=%d dim=%d vdim=%d rotated=%d",
+               Hq, Gk, Gv, dim, vdim, 2 * half);
+  if (T <= 0) return 0;
+  QkvNormTailParams p{d_proj, ldp, q_off, k_off, v_off, half > 0 ? d_cs : nullptr, half, layout, d_q_norm, d_k_norm, eps,
+                      d_q_out, d_k_cache, d_v_cache, d_row_req, d_pos, d_page_indptr, d_page_indices, page_size, Hq, Gk, Gv,
+                      dim, vdim};
+  if (dtype == 1) VB_LAUNCH_PDL(qkv_norm_rotary_append_kernel<float>, T, 256, 0, stream, p);
+  else VB_LAUNCH_PDL(qkv_norm_rotary_append_kernel<bf16>, T, 256, 0, stream, p);
+  return 0;
+}
+
+int vb_latent_rope_append(const float* d_proj, int ldp, int q_off, int c_off, int H, int dim, int rot, int kv_rank,
+                          const float* d_wc, const float* d_cs, int half, int layout, void* d_q_out, void* d_q_lat,
+                          void* d_cache, const int32_t* d_row_req, const int32_t* d_pos, const int32_t* d_page_indptr,
+                          const int32_t* d_page_indices, int page_size, int T, float eps, int dtype, void* stream) {
+  VB_CHECK_ARG(d_proj && d_wc && d_q_out && d_q_lat && d_cache && d_row_req && d_pos && d_page_indptr && d_page_indices,
+               "vb_latent_rope_append: null pointer");
+  VB_CHECK_ARG(H > 0 && dim >= 0 && rot >= 0 && dim + rot > 0 && kv_rank > 0 && page_size > 0 && half >= 0 && 2 * half <= rot &&
+               (layout == 0 || layout == 1) && q_off >= 0 && c_off >= 0 && q_off + H * (dim + rot) <= ldp &&
+               c_off + kv_rank + rot <= ldp, "vb_latent_rope_append: bad sizes H=%d dim=%d rot=%d kv_rank=%d rotated=%d",
+               H, dim, rot, kv_rank, 2 * half);
+  if (T <= 0) return 0;
+  LatentRopeTailParams p{d_proj, ldp, q_off, c_off, H, dim, rot, kv_rank, d_wc, half > 0 ? d_cs : nullptr, half, layout,
+                         d_q_out, d_q_lat, d_cache, d_row_req, d_pos, d_page_indptr, d_page_indices, page_size, eps};
+  if (dtype == 1) VB_LAUNCH_PDL(latent_rope_append_kernel<float>, T, 128, 0, stream, p);
+  else VB_LAUNCH_PDL(latent_rope_append_kernel<bf16>, T, 128, 0, stream, p);
+  return 0;
+}
+
+int vb_head_pair_combine(void* d_out, const float* d_a, const float* d_gate, int ld_gate, int T, int H, int R, int vdim,
+                         float lambda, float post, float eps, int dtype, void* stream) {
+  VB_CHECK_ARG(d_out && d_a && H > 0 && R > 0 && H % R == 0 && vdim > 0, "vb_head_pair_combine: bad arguments");
+  if (T <= 0) return 0;
+  const int grid = (T * H + 3) / 4;
+  if (dtype == 1)
+    VB_LAUNCH_PDL(head_pair_combine_kernel<float>, grid, 128, 0, stream, static_cast<float*>(d_out), d_a, d_gate, ld_gate, T, H, R,
+                  vdim, lambda, post, eps);
+  else
+    VB_LAUNCH_PDL(head_pair_combine_kernel<bf16>, grid, 128, 0, stream, static_cast<bf16*>(d_out), d_a, d_gate, ld_gate, T, H, R,
+                  vdim, lambda, post, eps);
   return 0;
 }
 
@@ -822,18 +1048,25 @@ int vb_window_attn(void* d_out, const void* d_q, const void* d_k_cache, const vo
                    int ld_gate, const int32_t* d_row_req, const int32_t* d_pos, const int32_t* d_page_indptr,
                    const int32_t* d_page_indices, int T, int H, int G, int dim, int vdim, int page_size, int window,
                    float scale, int dtype, float* d_part, long long part_floats, const int32_t* d_row_list, int head_rows,
-                   void* stream) {
+                   int chunk, int k_ld, int v_ld, int v_share, int out_f32, void* stream) {
   VB_CHECK_ARG(d_out && d_q && d_k_cache && d_v_cache && d_row_req && d_pos && d_page_indptr && d_page_indices,
                "vb_window_attn: null pointer");
   VB_CHECK_ARG(H > 0 && G > 0 && H % G == 0 && dim > 0 && vdim > 0 && vdim <= 32 * WA_MAXU && page_size > 0,
                "vb_window_attn: bad sizes H=%d G=%d dim=%d vdim=%d (vdim <= %d)", H, G, dim, vdim, 32 * WA_MAXU);
   if (T <= 0) return 0;
+  if (v_share <= 0) v_share = 1;
+  VB_CHECK_ARG(G % v_share == 0, "vb_window_attn: %d key heads do not share value heads %d by %d", G, v_share, v_share);
+  if (k_ld <= 0) k_ld = G * dim;
+  if (v_ld <= 0) v_ld = (G / v_share) * vdim;
   WindowAttnParams p{d_q, d_k_cache, d_v_cache, d_out, d_gate, ld_gate, d_row_req, d_pos, d_page_indptr, d_page_indices,
-                     nullptr, nullptr, nullptr, T, H, G, dim, vdim, page_size, window, scale, d_row_list, 0, 1, d_part};
+                     nullptr, nullptr, nullptr, T, H, G, dim, vdim, page_size, window, chunk, k_ld, v_ld, v_share, out_f32,
+                     scale, d_row_list, 0, 1, d_part};
   const int R = H / G;
+  const bool mma_ok = dtype == 0 && dim % 16 == 0 && vdim % 16 == 0 && dim <= 16 * F_KB && vdim <= 8 * F_NT &&
+                      k_ld % 8 == 0 && v_ld % 8 == 0;
   // head_rows: the query heads that share a key/value head become the rows of a tensor-core tile (bf16, head sizes the
   // tile kernel takes, 2 .. 64 heads per group): the group's K / V tiles are staged once and multiplied on the tensor cores
-  if (head_rows && dtype == 0 && R >= 2 && R <= FM && dim % 16 == 0 && vdim % 16 == 0 && dim <= 16 * F_KB && vdim <= 8 * F_NT) {
+  if (head_rows && mma_ok && R >= 2 && R <= FM) {
     int splits = 1;
     if (d_part) {
       splits = max(1, min(8, (2 * 148) / max(1, T * G)));
@@ -886,16 +1119,21 @@ int vb_window_attn_tiled(void* d_out, const void* d_q, const void* d_k_cache, co
                          int ld_gate, const int32_t* d_pos, const int32_t* d_page_indptr, const int32_t* d_page_indices,
                          const int32_t* d_qo_indptr, const int32_t* d_tile_req, const int32_t* d_tile_row0, int n_tiles,
                          int T, int H, int G, int dim, int vdim, int page_size, int window, float scale, int dtype,
-                         void* stream) {
+                         int chunk, int k_ld, int v_ld, int v_share, int out_f32, void* stream) {
   VB_CHECK_ARG(d_out && d_q && d_k_cache && d_v_cache && d_pos && d_page_indptr && d_page_indices && d_qo_indptr &&
                d_tile_req && d_tile_row0, "vb_window_attn_tiled: null pointer");
   VB_CHECK_ARG(H > 0 && G > 0 && H % G == 0 && dim > 0 && vdim > 0 && vdim <= 4 * WT_MAXD && page_size > 0,
                "vb_window_attn_tiled: bad sizes H=%d G=%d dim=%d vdim=%d", H, G, dim, vdim);
   if (n_tiles <= 0) return 0;
+  if (v_share <= 0) v_share = 1;
+  VB_CHECK_ARG(G % v_share == 0, "vb_window_attn_tiled: %d key heads do not share value heads %d by %d", G, v_share, v_share);
+  if (k_ld <= 0) k_ld = G * dim;
+  if (v_ld <= 0) v_ld = (G / v_share) * vdim;
   WindowAttnParams p{d_q, d_k_cache, d_v_cache, d_out, d_gate, ld_gate, nullptr, d_pos, d_page_indptr, d_page_indices,
-                     d_qo_indptr, d_tile_req, d_tile_row0, T, H, G, dim, vdim, page_size, window, scale, nullptr, 0, 1, nullptr};
+                     d_qo_indptr, d_tile_req, d_tile_row0, T, H, G, dim, vdim, page_size, window, chunk, k_ld, v_ld, v_share,
+                     out_f32, scale, nullptr, 0, 1, nullptr};
   dim3 grid(n_tiles, H);
-  if (dtype == 0 && dim % 16 == 0 && vdim % 16 == 0 && dim <= 16 * F_KB && vdim <= 8 * F_NT) {
+  if (dtype == 0 && dim % 16 == 0 && vdim % 16 == 0 && dim <= 16 * F_KB && vdim <= 8 * F_NT && k_ld % 8 == 0 && v_ld % 8 == 0) {
     const size_t msmem = 2 * static_cast<size_t>(FN) * (dim + 8 + vdim + 8) * sizeof(__nv_bfloat16);      // two stages
     VB_CHECK_CUDA(cudaFuncSetAttribute(window_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
     VB_LAUNCH_PDL(window_attn_mma_kernel, grid, 128, msmem, stream, p);

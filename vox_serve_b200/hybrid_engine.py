@@ -43,17 +43,39 @@ BF16, F32, I32 = torch.bfloat16, torch.float32, torch.int32
 class RotaryConfig:
     dims: int
     base: float
-    factor: Optional[float] = None       # Llama-3.1 style wavelength-dependent scaling when set
+    factor: Optional[float] = None       # frequency scaling when set (``scaling`` says which kind)
     low: float = 1.0
     high: float = 4.0
     original: float = 8192.0
+    layout: str = "interleaved"          # "interleaved": dim 2i goes with 2i + 1; "half": dim i goes with i + dims / 2
+    scaling: str = "wavelength"          # "wavelength" (Llama-3.1 style, low / high) | "yarn" (fast / slow turns, ramp over the
+    #                                      pair index, cos and sin times 0.1 ln(factor) + 1)
+    fast: float = 32.0
+    slow: float = 1.0
 
     def key(self) -> Tuple:
-        return (self.dims, self.base, self.factor, self.low, self.high, self.original)
+        return (self.dims, self.base, self.factor, self.low, self.high, self.original, self.scaling, self.fast, self.slow)
+
+    def multiplier(self) -> float:
+        """What cos and sin are multiplied by."""
+        return 0.1 * math.log(self.factor) + 1.0 if (self.factor is not None and self.scaling == "yarn") else 1.0
 
     def frequencies(self) -> torch.Tensor:
-        """float64 [dims / 2]: base^(-2i/dims); wavelengths above original/low are slowed by ``factor``, those below
-        original/high kept, the band in between interpolated linearly in original/wavelength."""
+        """float64 [dims / 2]: base^(-2i/dims).  "wavelength" scaling: wavelengths above original/low are slowed by
+        ``factor``, those below original/high kept, the band in between interpolated linearly in original/wavelength.
+        "yarn" scaling: with d(t) = dims ln(original / (2 pi t)) / (2 ln base) the pair index that turns t times within
+        ``original`` positions, pairs up to lo = max(floor d(fast), 0) keep their frequency, pairs from
+        hi = min(ceil d(slow), dims - 1) on are slowed by ``factor``, linearly mixed in between."""
+        if self.factor is not None and self.scaling == "yarn":
+            def d(t):
+                return self.dims * math.log(self.original / (2.0 * math.pi * t)) / (2.0 * math.log(self.base))
+            lo, hi = max(math.floor(d(self.fast)), 0), min(math.ceil(d(self.slow)), self.dims - 1)
+            out = []
+            for i in range(self.dims // 2):
+                f = self.base ** (-2.0 * i / self.dims)
+                ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+                out.append(f / self.factor * ramp + f * (1.0 - ramp))
+            return torch.tensor(out, dtype=torch.float64)
         out = []
         for i in range(self.dims // 2):
             f = self.base ** (-2.0 * i / self.dims)
@@ -100,15 +122,54 @@ class LatentAttentionConfig:
     dim: int
     vdim: int
     kv_rank: int
-    q_rank: int
+    q_rank: int                           # 0: queries are projected from the sublayer's input directly (no query latent)
     scale: float
     kv_from: Optional[int] = None
+    # heads with a rotated part: every query head has rot_dim more dims behind its `dim` unrotated ones, and every token has
+    # ONE rotated key part of rot_dim dims shared by all heads, cached behind the latent ([kv_rank | rot_dim] per token)
+    rot_dim: int = 0
+    rotary: Optional[RotaryConfig] = None
+    head_gate: bool = True
+
+
+@dataclass
+class DiffAttentionConfig:
+    """Softmax attention with two score maps per head over the same values (queries and keys hold [map 1 | map 2] per head):
+    o = a1 - lambda * a2, divided by its root mean square over the head's vdim values, times (1 - diff); lambda is one number
+    per layer.  Queries and keys are RMS-normed per head and map (qk_norm) before the rotation; chunk > 0 restricts a position
+    to the keys of its own block of `chunk` positions; a sigmoid gate per output value."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    diff: float
+    chunk: int = 0
+    window: int = 0
+    rotary: Optional[RotaryConfig] = None
+    qk_norm: bool = True
+    gate: bool = True
+
+
+@dataclass
+class MinGRUConfig:
+    """Element-wise gated recurrence: S_t = (1 - z) S_(t-1) + z c with z = sigmoid(W_z h + b), c = u + 1/2 (u >= 0) or
+    sigmoid(u), u = W_x h + b; output W_o (S_t * silu(W_g h)); fp32 state of `width` values per request."""
+    width: int
 
 
 @dataclass
 class DenseMLPConfig:
     ff: int
     act: str = "relu2"                    # "relu2" | "gelu" | "gelu_tanh": down(act(up h))
+
+
+@dataclass
+class GluMLPConfig:
+    """down(g * sigmoid(slope * g) * (u + 1)) with g = min(gate h, limit), u = clamp(up h, -limit, limit)."""
+    ff: int
+    limit: float
+    slope: float = 1.702
 
 
 @dataclass
@@ -127,9 +188,9 @@ class MoEConfig:
 
 @dataclass
 class HybridLayerConfig:
-    kind: str                             # "attention" | "lightning" | "latent"
+    kind: str                             # "attention" | "lightning" | "latent" | "diff_attention" | "mingru"
     mixer: Any
-    mlp: Any = None                       # MoEConfig | DenseMLPConfig | None
+    mlp: Any = None                       # MoEConfig | DenseMLPConfig | GluMLPConfig | None
 
 
 @dataclass
@@ -140,11 +201,28 @@ class HybridConfig:
     logit_scale: float
     layers: List[HybridLayerConfig]
     block: str = "sequential"             # "sequential": x += LN(mixer(LN x)); x += LN(ff(LN x)).  "parallel": x += m * (mixer(n1 x) + ff(n2 x))
-    norm: str = "layernorm"               # "layernorm" (weight and bias) | "rmsnorm" (weight)
+    #                                       "gated": pre-norm, x += sigmoid(W_r h + b) * sublayer(h) with h = norm(x), mixer then ff
+    norm: str = "layernorm"               # "layernorm" (weight and bias) | "rmsnorm" (weight) | "rmsnorm_scalar" (one number)
     residual_mult: float = 1.0            # m of the parallel form
     positions: int = 0                    # rows of the learned position table added to the embedding (0: none)
     side_dim: int = 0                     # per-token side input of every block (parallel form): dims per layer (0: none)
     logit_softcap: float = 0.0            # logits <- cap * tanh(logits / cap) (0: none)
+    embed_scale: float = 1.0              # the embedding rows are multiplied by this
+    # layers loop_start .. loop_stop - 1 run loop_times times in a row with the same weights; every pass has its own cache and
+    # state, and before each pass but the first the embedding output is added to the stream
+    loop_start: int = 0
+    loop_stop: int = 0
+    loop_times: int = 1
+
+    def runs(self) -> List[Tuple[int, bool]]:
+        """(layer index, does a repeated pass start here) for every layer run in order.  Caches and states are kept per run."""
+        n, a, b = len(self.layers), self.loop_start, self.loop_stop
+        if b <= a:
+            return [(i, False) for i in range(n)]
+        out = [(i, False) for i in range(a)]
+        for r in range(self.loop_times):
+            out += [(i, r > 0 and i == a) for i in range(a, b)]
+        return out + [(i, False) for i in range(b, n)]
 
     @classmethod
     def from_json(cls, c: Dict[str, Any]) -> "HybridConfig":
@@ -232,6 +310,10 @@ class HybridWeights:
         if cfg.norm == "rmsnorm":
             def norm(name):                                        # noqa: F811  (weight only)
                 return vec(name), None
+        elif cfg.norm == "rmsnorm_scalar":
+            def norm(name):                                        # noqa: F811  (one number, kept as a constant vector)
+                return vec(name).reshape(1).expand(cfg.width).contiguous(), None
+        self._gate_up = gate_up
         self.embed = mat("embed")
         self.head = dense(mat("head"))
         self.final_norm = norm("final.norm")
@@ -252,6 +334,9 @@ class HybridWeights:
         for i, L in enumerate(cfg.layers):
             p = f"l{i}."
             m = L.mixer
+            if cfg.block == "gated":
+                self.layers.append(self._load_gated_layer(sd, p, i, L, norm))
+                continue
             if cfg.block == "parallel":
                 w: Dict[str, Any] = {"norm1": vec(p + "norm1")}
                 if L.mlp is not None:
@@ -319,7 +404,75 @@ class HybridWeights:
                         w["s_gu"] = gate_up(p + "mlp.shared.gate", p + "mlp.shared.up")
                         w["s_down"] = dense(mat(p + "mlp.shared.down"))
             self.layers.append(w)
-        del self._mat, self._vec, self._dense
+        del self._mat, self._vec, self._dense, self._gate_up
+
+    def _load_gated_layer(self, sd, p: str, i: int, L: "HybridLayerConfig", norm) -> Dict[str, Any]:
+        """A pre-norm layer with gated residuals: ``l<i>.norm1`` / ``norm2``, ``l<i>.rg1[.b]`` / ``rg2[.b]`` (the gates of the
+        mixer's and the feed-forward's residual), ``l<i>.mix.*``, ``l<i>.mlp.{gate,up,down}``.  The mixer's gate reads the
+        mixer's input, so its matrix is stacked under the mixer's own input projections ("in": ONE projection per mixer).
+          latent attention without a query latent: in = q | dkv | rg1; uk per head transposed, uv per head
+          attention with two score maps: in = q | k | v | g | rg1, the query heads reordered per key/value group as
+            [map 1 of the group's heads | map 2 of them] so that a query head's key head is (head index) / (heads per group)
+          minGRU: in = z | x | g | rg1, biases of z and x in fp32"""
+        mat, vec, dense, cfg, W, m = self._mat, self._vec, self._dense, self.cfg, self.cfg.width, L.mixer
+        w: Dict[str, Any] = {"norm1": norm(p + "norm1")[0], "rg1_b": vec(p + "rg1.b")}
+        rg1 = mat(p + "rg1")
+        if tuple(rg1.shape) != (W, W):
+            raise VoxB200Error(f"layer {i}: residual gate shape does not match the configuration")
+        if L.kind == "latent":
+            if m.q_rank or m.kv_from is not None or m.head_gate:
+                raise VoxB200Error(f"layer {i}: gated blocks take latent attention with direct queries, own latents and no head gate")
+            dq = m.dim + m.rot_dim
+            q, dkv = mat(p + "mix.q"), mat(p + "mix.dkv")
+            uk, uv, o = mat(p + "mix.uk"), mat(p + "mix.uv"), mat(p + "mix.o")
+            if (tuple(q.shape) != (m.heads * dq, W) or tuple(dkv.shape) != (m.kv_rank + m.rot_dim, W) or
+                    tuple(uk.shape) != (m.heads * m.dim, m.kv_rank) or tuple(uv.shape) != (m.heads * m.vdim, m.kv_rank) or
+                    tuple(o.shape) != (W, m.heads * m.vdim)):
+                raise VoxB200Error(f"layer {i}: latent attention shapes do not match the configuration")
+            w["in"] = dense(torch.cat([q, dkv, rg1], 0).contiguous())
+            w["dkv_norm"] = vec(p + "mix.dkv.norm")
+            w["uk_t"] = uk.view(m.heads, m.dim, m.kv_rank).transpose(1, 2).contiguous()
+            w["uv"] = uv.view(m.heads, m.vdim, m.kv_rank).contiguous()
+            w["o"] = dense(o)
+        elif L.kind == "diff_attention":
+            H, G, D, V = m.heads, m.kv_heads, m.dim, m.vdim
+            q, k, v, o = mat(p + "mix.q"), mat(p + "mix.k"), mat(p + "mix.v"), mat(p + "mix.o")
+            if (tuple(q.shape) != (H * 2 * D, W) or tuple(k.shape) != (G * 2 * D, W) or tuple(v.shape) != (G * V, W) or
+                    tuple(o.shape) != (W, H * V)):
+                raise VoxB200Error(f"layer {i}: attention shapes do not match the configuration")
+            q = q.view(G, H // G, 2, D, W).permute(0, 2, 1, 3, 4).reshape(H * 2 * D, W)
+            parts = [q, k, v]
+            if m.gate:
+                g = mat(p + "mix.g")
+                if tuple(g.shape) != (H * V, W):
+                    raise VoxB200Error(f"layer {i}: attention gate shape does not match the configuration")
+                parts.append(g)
+            w["in"] = dense(torch.cat(parts + [rg1], 0).contiguous())
+            w["o"] = dense(o)
+            if m.qk_norm:
+                w["q_norm"], w["k_norm"] = vec(p + "mix.q.norm"), vec(p + "mix.k.norm")
+            lam = [sd[p + "mix." + n].to(torch.float64) for n in ("lq1", "lk1", "lq2", "lk2")]
+            w["lambda"] = float(torch.exp((lam[0] * lam[1]).sum()) - torch.exp((lam[2] * lam[3]).sum()) + m.diff)
+        elif L.kind == "mingru":
+            z, x, g, o = mat(p + "mix.z"), mat(p + "mix.x"), mat(p + "mix.g"), mat(p + "mix.o")
+            if any(tuple(t.shape) != (m.width, W) for t in (z, x, g)) or tuple(o.shape) != (W, m.width):
+                raise VoxB200Error(f"layer {i}: minGRU shapes do not match the configuration")
+            w["in"] = dense(torch.cat([z, x, g, rg1], 0).contiguous())
+            w["z_b"], w["x_b"] = vec(p + "mix.z.b"), vec(p + "mix.x.b")
+            w["o"] = dense(o)
+        else:
+            raise VoxB200Error(f"layer {i}: mixer '{L.kind}' is not available in gated blocks")
+        f = L.mlp
+        if f is not None:
+            if not isinstance(f, GluMLPConfig):
+                raise VoxB200Error(f"layer {i}: gated blocks take the clamped gated feed-forward")
+            w["norm2"], w["rg2_b"] = norm(p + "norm2")[0], vec(p + "rg2.b")
+            if (tuple(sd[p + "mlp.gate"].shape) != (f.ff, W) or tuple(sd[p + "mlp.up"].shape) != (f.ff, W) or
+                    tuple(sd[p + "mlp.down"].shape) != (W, f.ff) or tuple(sd[p + "rg2"].shape) != (W, W)):
+                raise VoxB200Error(f"layer {i}: feed-forward shapes do not match the configuration")
+            w["gu"] = self._gate_up(p + "mlp.gate", p + "mlp.up")
+            w["down"], w["rg2"] = dense(mat(p + "mlp.down")), dense(mat(p + "rg2"))
+        return w
 
     def _load_latent(self, sd, p: str, i: int, m: "LatentAttentionConfig", w: Dict[str, Any]) -> None:
         """``l<i>.mix.{dq, dq.norm, uq, dkv, dkv.norm, uk, uv, g, o}``: dq | dkv | g become one projection (a layer that
@@ -405,8 +558,10 @@ class HybridWeights:
 class HybridCache:
     """Per attention layer K [pages, page, G, dim] and V [pages, page, G, vdim] in the compute dtype (all layers share
     one page table: page p of every layer belongs to the same request); per latent-attention layer that projects its own
-    latents ONE tensor [pages, page, 1, kv_rank] that is both K and V (a layer reading another layer's latents aliases
-    that layer's tensor); per linear-attention layer a state [slots, H, dim, vdim] in fp32.  Pages and slots are handed out by the worker; a slot's state is treated as zero by
+    latents ONE tensor [pages, page, 1, kv_rank (+ rot_dim)] that is both K and V (a layer reading another layer's latents aliases
+    that layer's tensor); per attention layer with two score maps K [pages, page, 2 G, dim] and V [pages, page, G, vdim];
+    per linear-attention layer a state [slots, H, dim, vdim] and per minGRU layer a state [slots, width] in fp32.  A layer
+    that a loop runs several times has one of these per pass.  Pages and slots are handed out by the worker; a slot's state is treated as zero by
     the kernels when its request starts at position 0, so nothing is cleared on reuse."""
 
     def __init__(self, cfg: HybridConfig, num_pages: int, page_size: int, num_slots: int, dtype: torch.dtype, device):
@@ -414,16 +569,24 @@ class HybridCache:
         self.k: Dict[int, torch.Tensor] = {}
         self.v: Dict[int, torch.Tensor] = {}
         self.state: Dict[int, torch.Tensor] = {}
-        for i, L in enumerate(cfg.layers):
+        # one entry per layer RUN (a layer inside a loop runs several times, each pass with a cache or state of its own);
+        # without a loop the run index is the layer index
+        for i, (li, _) in enumerate(cfg.runs()):
+            L = cfg.layers[li]
             m = L.mixer
             if L.kind == "attention":
                 self.k[i] = torch.zeros(num_pages, page_size, m.kv_heads, m.dim, dtype=dtype, device=device)
                 self.v[i] = torch.zeros(num_pages, page_size, m.kv_heads, m.vdim, dtype=dtype, device=device)
+            elif L.kind == "diff_attention":                      # two key maps per key/value head, one value head
+                self.k[i] = torch.zeros(num_pages, page_size, 2 * m.kv_heads, m.dim, dtype=dtype, device=device)
+                self.v[i] = torch.zeros(num_pages, page_size, m.kv_heads, m.vdim, dtype=dtype, device=device)
             elif L.kind == "latent":
-                if m.kv_from is None:
-                    self.k[i] = self.v[i] = torch.zeros(num_pages, page_size, 1, m.kv_rank, dtype=dtype, device=device)
+                if m.kv_from is None:                             # [latent | shared rotated key part]
+                    self.k[i] = self.v[i] = torch.zeros(num_pages, page_size, 1, m.kv_rank + m.rot_dim, dtype=dtype, device=device)
                 else:
                     self.k[i] = self.v[i] = self.k[m.kv_from]
+            elif L.kind == "mingru":
+                self.state[i] = torch.zeros(num_slots, m.width, dtype=F32, device=device)
             else:
                 self.state[i] = torch.zeros(num_slots, m.heads, m.dim, m.vdim, dtype=F32, device=device)
 
@@ -466,27 +629,47 @@ class HybridEngine:
         att = [L.mixer for L in cfg.layers if L.kind == "attention"]
         lin = [L.mixer for L in cfg.layers if L.kind == "lightning"]
         lat = [L.mixer for L in cfg.layers if L.kind == "latent"]
+        dif = [L.mixer for L in cfg.layers if L.kind == "diff_attention"]
+        gru = [L.mixer for L in cfg.layers if L.kind == "mingru"]
         moe = [L.mlp for L in cfg.layers if isinstance(L.mlp, MoEConfig)]
-        dmlp = [L.mlp for L in cfg.layers if isinstance(L.mlp, DenseMLPConfig)]
+        dmlp = [L.mlp for L in cfg.layers if isinstance(L.mlp, (DenseMLPConfig, GluMLPConfig))]
+        gated = W if cfg.block == "gated" else 0          # the residual gate's columns ride on the mixer's input projection
         p_att = [m.heads * m.dim + m.kv_heads * (m.dim + m.vdim) + m.heads * m.vdim for m in att]
         p_lin = [2 * m.heads * (m.dim + m.vdim) for m in lin]
-        p_lat = [m.q_rank + m.kv_rank + m.heads for m in lat]
-        hv = max([m.heads * m.vdim for m in att + lin + lat] + [1])
+        p_lat = [(m.q_rank if m.q_rank else m.heads * (m.dim + m.rot_dim)) + m.kv_rank + m.rot_dim + m.heads + gated for m in lat]
+        p_dif = [2 * (m.heads + m.kv_heads) * m.dim + m.kv_heads * m.vdim + m.heads * m.vdim + gated for m in dif]
+        p_gru = [3 * m.width + gated for m in gru]
+        hv = max([m.heads * m.vdim for m in att + lin + lat + dif] + [m.width for m in gru] + [1])
         for m in lat:
             if m.kv_rank > 256:
                 raise VoxB200Error(f"latent attention: kv_rank {m.kv_rank} exceeds the 256 dims the attention kernels take per head")
+            if m.rot_dim and (m.rotary is not None and (m.rotary.dims > m.rot_dim or m.rotary.dims % 2)):
+                raise VoxB200Error(f"rotary dims {m.rotary.dims} do not fit the rotated part of {m.rot_dim} dims")
+        for m in dif:
+            if m.heads % m.kv_heads or m.vdim > 256:
+                raise VoxB200Error(f"attention: {m.heads} heads on {m.kv_heads} key/value heads of {m.vdim} values "
+                                   "(heads a multiple of key/value heads, at most 256 values per head)")
         self.x = torch.zeros(R, W, dtype=F32, device=dev)              # residual stream
         self.h = torch.zeros(R, W, dtype=CT, device=dev)               # normed input of the running sublayer
         self.y = torch.zeros(R, W, dtype=F32, device=dev)              # sublayer output
-        self.proj = torch.zeros(R * max(p_att + p_lin + p_lat + [1]), dtype=F32, device=dev)
-        self.q = torch.zeros(R * max([m.heads * m.dim for m in att + lat] + [1]), dtype=CT, device=dev)
+        self.proj = torch.zeros(R * max(p_att + p_lin + p_lat + p_dif + p_gru + [1]), dtype=F32, device=dev)
+        self.q = torch.zeros(R * max([m.heads * m.dim for m in att + lat] + [2 * m.heads * m.dim for m in dif] + [1]),
+                             dtype=CT, device=dev)
+        if cfg.block == "gated":
+            self.rg = torch.zeros(R, W, dtype=F32, device=dev)         # the feed-forward's residual gate before its sigmoid
+            # the embedding output, added again before every repeated pass over the looped layers
+            self.e0 = torch.zeros(R, W, dtype=F32, device=dev) if any(r for _, r in cfg.runs()) else None
+        if dif:
+            self.pair_o = torch.zeros(R * max(2 * m.heads * m.vdim for m in dif), dtype=F32, device=dev)   # both maps' outputs
+        if gru:
+            self.gru_scratch = None
         if cfg.block == "parallel":
             self.h2 = torch.zeros(R, W, dtype=CT, device=dev)          # the feed-forward's norm of the same stream
             self.y2 = torch.zeros(R, W, dtype=F32, device=dev)         # the feed-forward's output
         if lat:
             self.cq = torch.zeros(R * max(m.q_rank for m in lat), dtype=CT, device=dev)            # normed query latent
-            n_lat = R * max(m.heads * m.kv_rank for m in lat)
-            self.q_lat = torch.zeros(n_lat, dtype=CT, device=dev)      # queries carried into latent space
+            n_lat = R * max(m.heads * (m.kv_rank + m.rot_dim) for m in lat)
+            self.q_lat = torch.zeros(n_lat, dtype=CT, device=dev)      # queries carried into latent space (+ their rotated parts)
             self.o_lat = torch.zeros(n_lat, dtype=CT, device=dev)      # attention output in latent space
         if dmlp:
             self.ff_act = torch.zeros(R * max(f.ff for f in dmlp), dtype=CT, device=dev)
@@ -500,18 +683,25 @@ class HybridEngine:
         if tiled:
             n_t = max_rows // self.lin_tile_rows + max_out_rows + 1
             self.lin_scratch = torch.zeros(n_t * max(m.heads * m.dim * m.vdim for m in tiled), dtype=F32, device=dev)
+        if gru:
+            n_t = max_rows // self.lin_tile_rows + max_out_rows + 1
+            self.gru_scratch = torch.zeros(n_t * 2 * max(m.width for m in gru), dtype=F32, device=dev)
         self.v_first = torch.zeros(R * max([m.kv_heads * m.vdim for m in att if m.v_mix] + [1]), dtype=F32, device=dev)
         # split-key scratch of the per-row attention kernel: steps of up to 256 rows, 8 splits
         self.attn_part = torch.zeros(256 * 8 * max([m.heads * (m.vdim + 2) for m in att] +
+                                                   [2 * m.heads * (m.vdim + 2) for m in dif] +
                                                    [m.heads * (m.kv_rank + 2) for m in lat] + [1]), dtype=F32, device=dev)
         self.freqs: Dict[Tuple, torch.Tensor] = {}
         self.cs: Dict[Tuple, torch.Tensor] = {}
-        for m in att:
-            if m.rotary is not None and m.rotary.key() not in self.freqs:
-                if m.rotary.dims > m.dim or m.rotary.dims % 2:
-                    raise VoxB200Error(f"rotary dims {m.rotary.dims} do not fit head dim {m.dim}")
-                self.freqs[m.rotary.key()] = m.rotary.frequencies().to(dev)
-                self.cs[m.rotary.key()] = torch.zeros(R, 2, m.rotary.dims // 2, dtype=F32, device=dev)
+        self.cs_mult: Dict[Tuple, float] = {}
+        for m in att + dif + lat:
+            rot = getattr(m, "rotary", None)
+            if rot is not None and rot.key() not in self.freqs:
+                if (m not in lat and rot.dims > m.dim) or rot.dims % 2:
+                    raise VoxB200Error(f"rotary dims {rot.dims} do not fit head dim {m.dim}")
+                self.freqs[rot.key()] = rot.frequencies().to(dev)
+                self.cs[rot.key()] = torch.zeros(R, 2, rot.dims // 2, dtype=F32, device=dev)
+                self.cs_mult[rot.key()] = rot.multiplier()
         if moe:
             top, E = max(f.top for f in moe), max(f.experts for f in moe)
             # grouped tensor-core form: row tiles of GROUP_TILE rows, every expert's rows padded to whole tiles
@@ -537,6 +727,7 @@ class HybridEngine:
         self.first_vmix = next((i for i, L in enumerate(cfg.layers) if L.kind == "attention" and L.mixer.v_mix), None)
         self.layer_tap = None          # set to a list: the residual stream after every layer is appended (tests)
         self.use_tiled_attention = True
+        self.use_tiled_recurrence = True
 
     GROUP_TILE = 128          # rows per tile of the grouped expert projections
     GROUPED_MIN_ROWS = 512    # steps with at least this many rows run the experts grouped; smaller ones in the dense form
@@ -567,18 +758,19 @@ class HybridEngine:
 
     # ---- mixers ----------------------------------------------------------------------------------------------
     def _run_attention(self, s: StepInputs, q, kc, vc, out, gate, H: int, G: int, dim: int, vdim: int, window: int,
-                       scale: float, head_rows: bool = False) -> None:
-        """Prompt portions on the tiled kernel and single-token rows on the per-row kernel (split over keys with few rows)."""
+                       scale: float, head_rows: bool = False, **kw) -> None:
+        """Prompt portions on the tiled kernel and single-token rows on the per-row kernel (split over keys with few rows).
+        kw: chunk, k_ld, v_ld, v_share of ``ops.window_attn``."""
         tiles = None
         if s.tiles is not None and self.use_tiled_attention and vdim <= 256:
             tiles = (s.qo_indptr, s.tiles[0], s.tiles[1], s.tiles[2])
         args = (q, kc, vc, out, gate, s.row_req, s.pos, s.page_indptr, s.page_indices, s.T, H, G, dim, vdim, window, scale)
         if tiles is not None and (not s.single or s.single_rows is not None):
-            ops.window_attn(*args, tiles=tiles)
+            ops.window_attn(*args, tiles=tiles, **kw)
             if s.single:
-                ops.window_attn(*args, scratch=self.attn_part, rows=s.single_rows, head_rows=head_rows)
+                ops.window_attn(*args, scratch=self.attn_part, rows=s.single_rows, head_rows=head_rows, **kw)
         else:
-            ops.window_attn(*args, scratch=self.attn_part, head_rows=head_rows)
+            ops.window_attn(*args, scratch=self.attn_part, head_rows=head_rows, **kw)
 
     def _latent(self, i: int, m: LatentAttentionConfig, w: Dict[str, Any], s: StepInputs) -> torch.Tensor:
         """Latent attention in its absorbed form: a head's score q . (U_k c) equals (U_k^T q) . c and its output
@@ -749,10 +941,12 @@ class HybridEngine:
             raise VoxB200Error(f"step of {T} rows / {s.n_out} logit rows exceeds the engine's {self.max_rows} / {self.max_out_rows}")
         if cfg.block == "parallel":
             return self._forward_parallel(s)
+        if cfg.block == "gated":
+            return self._forward_gated(s)
         x, h, y = self.x[:T], self.h[:T], self.y[:T]
-        ops.embed_rows_f32(w.embed, s.ids, x, w.pos, s.pos if w.pos is not None else None)
+        ops.embed_rows_f32(w.embed, s.ids, x, w.pos, s.pos if w.pos is not None else None, scale=cfg.embed_scale)
         for key, freq in self.freqs.items():
-            ops.rotary_table(s.pos, freq, self.cs[key][:T])
+            ops.rotary_table(s.pos, freq, self.cs[key][:T], self.cs_mult[key])
         eps = cfg.eps
         n = len(cfg.layers)
         if n:
@@ -785,7 +979,7 @@ class HybridEngine:
         hn = self.hn[:s.n_out]
         packed = isinstance(w.head, ops.PackedWeight)
         nw, nb = w.final_norm_scaled if packed else w.final_norm
-        if cfg.norm == "rmsnorm":
+        if cfg.norm != "layernorm":
             ops.rmsnorm2_f32(self.x, nw, cfg.eps, hn, rows=s.out_rows)
         else:
             ops.layernorm_f32(self.x, nw, nb, cfg.eps, hn, rows=s.out_rows)
@@ -799,7 +993,7 @@ class HybridEngine:
         x += m * (mixer(norm1 x) + ff(norm2 x)), then the per-token side input, fused with the next block's norms."""
         cfg, w, T = self.cfg, self.w, s.T
         x, h1, h2, eps = self.x[:T], self.h[:T], self.h2[:T], cfg.eps
-        ops.embed_rows_f32(w.embed, s.ids, x, w.pos, s.pos if w.pos is not None else None)
+        ops.embed_rows_f32(w.embed, s.ids, x, w.pos, s.pos if w.pos is not None else None, scale=cfg.embed_scale)
         n = len(cfg.layers)
         if n:
             ops.rmsnorm2_f32(x, w.layers[0]["norm1"], eps, h1, w.layers[0].get("norm2"), h2 if "norm2" in w.layers[0] else None)
@@ -821,3 +1015,125 @@ class HybridEngine:
             if self.layer_tap is not None:
                 self.layer_tap.append(x.clone())
         return self._head(s)
+
+    # ---- pre-norm blocks with gated residuals ------------------------------------------------------------------
+    def _forward_gated(self, s: StepInputs) -> torch.Tensor:
+        """x += sigmoid(W_r h + b) * mixer(h) with h = norm1(x), then the same with the feed-forward on norm2(x).  A layer
+        inside the loop runs once per pass on that pass's cache or state; before every pass but the first the embedding
+        output is added to the stream.  The residual update, that addition and the norm feeding the next sublayer are one
+        kernel (``gated_residual_norm_f32``)."""
+        cfg, w, T = self.cfg, self.w, s.T
+        x, h, eps = self.x[:T], self.h[:T], cfg.eps
+        runs = cfg.runs()
+        e0 = self.e0[:T] if self.e0 is not None else None
+        ops.embed_rows_f32(w.embed, s.ids, x, scale=cfg.embed_scale, out2=e0)
+        for key, freq in self.freqs.items():
+            ops.rotary_table(s.pos, freq, self.cs[key][:T], self.cs_mult[key])
+        if runs:
+            ops.rmsnorm2_f32(x, w.layers[runs[0][0]]["norm1"], eps, h)
+        for ri, (i, _) in enumerate(runs):
+            L, lw = cfg.layers[i], w.layers[i]
+            nxt = runs[ri + 1] if ri + 1 < len(runs) else None
+            y, r = self._gated_mixer(ri, L, lw, s)
+            if L.mlp is not None:
+                ops.gated_residual_norm_f32(x, y, r, lw["rg1_b"], eps, out=h, w=lw["norm2"])
+                y, r = self._glu_mlp(L.mlp, lw, h)
+            self._gated_tail(x, y, r, lw["rg2_b" if L.mlp is not None else "rg1_b"], nxt, e0, h)
+        return self._head(s)
+
+    def _gated_tail(self, x, y, r, bias, nxt, e0, h) -> None:
+        """The last residual update of a layer run, the embedding re-entering before a repeated pass, the next run's norm."""
+        eps = self.cfg.eps
+        nw = self.w.layers[nxt[0]]["norm1"] if nxt is not None else None
+        add = e0 if (nxt is not None and nxt[1]) else None
+        if self.layer_tap is None or add is None:
+            ops.gated_residual_norm_f32(x, y, r, bias, eps, out=h if nw is not None else None, w=nw, add=add)
+            if self.layer_tap is not None:
+                self.layer_tap.append(x.clone())
+            return
+        ops.gated_residual_norm_f32(x, y, r, bias, eps)                 # (tapped: the stream as the layer leaves it)
+        self.layer_tap.append(x.clone())
+        ops.gated_residual_norm_f32(x, add, None, None, eps, out=h, w=nw)
+
+    def _gated_mixer(self, ci: int, L: HybridLayerConfig, lw: Dict[str, Any], s: StepInputs):
+        """-> (mixer output fp32 [T, W], the residual gate's pre-activation: the last W columns of the input projection)."""
+        T, W, m = s.T, self.cfg.width, L.mixer
+        if L.kind == "latent":
+            P = m.heads * (m.dim + m.rot_dim) + m.kv_rank + m.rot_dim + W
+        elif L.kind == "diff_attention":
+            P = 2 * (m.heads + m.kv_heads) * m.dim + m.kv_heads * m.vdim + (m.heads * m.vdim if m.gate else 0) + W
+        else:
+            P = 3 * m.width + W
+        proj = self._proj(self.h[:T], lw["in"], self.proj[:T * P].view(T, P))
+        if L.kind == "latent":
+            y = self._latent_direct(ci, m, lw, s, proj)
+        elif L.kind == "diff_attention":
+            y = self._diff_attention(ci, m, lw, s, proj)
+        else:
+            y = self._mingru(ci, m, lw, s, proj)
+        return y, proj[:, P - W:]
+
+    def _latent_direct(self, ci: int, m: LatentAttentionConfig, w: Dict[str, Any], s: StepInputs, proj: torch.Tensor) -> torch.Tensor:
+        """Latent attention whose queries come straight from the input and whose heads have a rotated part, in the absorbed
+        form: a head's score q_u . (U_k c) + q_r . k_r equals [U_k^T q_u | q_r] . [c | k_r], so the cached rows [c | k_r]
+        serve every head as ONE key head of kv_rank + rot_dim dims whose leading kv_rank dims are also the value; the
+        per-head value expansion U_v runs on the latent-space output."""
+        T, H, R, D, Rd = s.T, m.heads, m.kv_rank, m.dim, m.rot_dim
+        cache = self.cache.k[ci]
+        q = self.q[:T * H * D].view(T, H, D)
+        q_lat = self.q_lat[:T * H * (R + Rd)].view(T, H, R + Rd)
+        cs, half = (self.cs[m.rotary.key()], m.rotary.dims // 2) if (m.rotary is not None and Rd) else (None, 0)
+        ops.latent_rope_append(proj, 0, H * (D + Rd), H, D, Rd, R, w["dkv_norm"], cs, half,
+                               m.rotary.layout if m.rotary is not None else "interleaved", q, q_lat, cache, s.row_req, s.pos,
+                               s.page_indptr, s.page_indices, T, self.cfg.eps)
+        ops.linear_batched(q, w["uk_t"], q_lat[:, :, :R])
+        o_lat = self.o_lat[:T * H * R].view(T, H * R)
+        self._run_attention(s, q_lat.view(T, H * (R + Rd)), cache, cache, o_lat, None, H, 1, R + Rd, R, 0, m.scale, head_rows=True,
+                            k_ld=R + Rd, v_ld=R + Rd)
+        out = self.mix_out[:T * H * m.vdim].view(T, H, m.vdim)
+        ops.linear_batched(o_lat.view(T, H, R), w["uv"], out)
+        return self._proj(out.view(T, H * m.vdim), w["o"], self.y[:T])
+
+    def _diff_attention(self, ci: int, m: DiffAttentionConfig, w: Dict[str, Any], s: StepInputs, proj: torch.Tensor) -> torch.Tensor:
+        """Both score maps of every head run as heads of their own through the attention kernels (2 H query heads on 2 G key
+        heads, consecutive key heads sharing a value head), leaving fp32 outputs that ``head_pair_combine`` subtracts,
+        norms and gates."""
+        T, H, G, D, V = s.T, m.heads, m.kv_heads, m.dim, m.vdim
+        nq, nk, nv = 2 * H * D, 2 * G * D, G * V
+        cs, half = (self.cs[m.rotary.key()], m.rotary.dims // 2) if m.rotary is not None else (None, 0)
+        q = self.q[:T * nq].view(T, nq)
+        kc, vc = self.cache.k[ci], self.cache.v[ci]
+        ops.qkv_norm_rotary_append(proj, 0, nq, nq + nk, cs, half, m.rotary.layout if m.rotary is not None else "half",
+                                   w.get("q_norm"), w.get("k_norm"), self.cfg.eps, q, kc, vc, s.row_req, s.pos, s.page_indptr,
+                                   s.page_indices, T, 2 * H)
+        pair = self.pair_o[:T * 2 * H * V].view(T, 2 * H * V)
+        self._run_attention(s, q, kc, vc, pair, None, 2 * H, 2 * G, D, V, m.window, m.scale, chunk=m.chunk, v_share=2)
+        out = self.mix_out[:T * H * V].view(T, H * V)
+        gate = proj[:, nq + nk + nv:nq + nk + nv + H * V] if m.gate else None
+        ops.head_pair_combine(pair, out, gate, H, H // G, V, w["lambda"], 1.0 - m.diff, self.cfg.eps)
+        return self._proj(out, w["o"], self.y[:T])
+
+    def _mingru(self, ci: int, m: MinGRUConfig, w: Dict[str, Any], s: StepInputs, proj: torch.Tensor) -> torch.Tensor:
+        T, Wm = s.T, m.width
+        out = self.mix_out[:T * Wm].view(T, Wm)
+        state = self.cache.state[ci]
+        par = (s.multi and s.tiles is not None and self.use_tiled_recurrence
+               and s.tiles[2] * 2 * Wm <= self.gru_scratch.numel())
+        if s.single or (s.multi and not par):
+            ops.mingru(proj, 0, Wm, 2 * Wm, w["z_b"], w["x_b"], state, out, s.qo_indptr, s.pos, s.slots, s.B,
+                       single_rows=s.single, multi_rows=s.multi and not par)
+        if par:
+            ops.mingru_tiled(proj, 0, Wm, 2 * Wm, w["z_b"], w["x_b"], state, out, self.gru_scratch, s.qo_indptr, s.pos, s.slots,
+                             s.tiles[0], s.tiles[1], s.tiles[2], self.lin_tile_rows, s.B)
+        return self._proj(out, w["o"], self.y[:T])
+
+    def _glu_mlp(self, f: GluMLPConfig, w: Dict[str, Any], h: torch.Tensor):
+        """-> (down(g * sigmoid(slope g) * (u + 1)), the residual gate's pre-activation W_r h)."""
+        T = h.shape[0]
+        act = self.ff_act[:T * f.ff].view(T, f.ff)
+        if isinstance(w["gu"], ops.PackedWeight):
+            ops.gemm_glu(h, w["gu"], act, f.limit, f.slope)
+        else:
+            ops.linear(h, w["gu"], act, epilogue=1, glu=(f.limit, f.slope))
+        r = self._proj(h, w["rg2"], self.rg[:T])
+        return self._proj(act, w["down"], self.y[:T]), r

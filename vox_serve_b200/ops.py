@@ -480,6 +480,17 @@ def gemm(x, w, mode: int = 0, split_k: int = 1, out=None, tile_rows: int = 128, 
     return out
 
 
+def gemm_glu(x: torch.Tensor, w: "PackedWeight", out: torch.Tensor, limit: float, slope: float) -> torch.Tensor:
+    """out bf16 [T, N / 2] = g * sigmoid(slope * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit); w: gate
+    and up rows interleaved per tile (interleave_gate_up) and packed."""
+    _need_cuda(x, out)
+    assert x.dtype == BF16 and x.dim() == 2 and x.shape[1] == w.K and out.dtype == BF16 and out.is_contiguous()
+    T = x.shape[0]
+    call("vb_gemm_bf16_glu", out.data_ptr(), w.data.data_ptr(), tensor_map_2d(x, gemm_t_tile(T)).ptr, T, w.N, w.K, out.shape[1],
+         w.tile_rows, out.shape[1], float(limit), float(slope), _stream())
+    return out
+
+
 def norm_lmhead(hidden: torch.Tensor, norm_weight: torch.Tensor, eps: float, w, bias: Optional[torch.Tensor] = None,
                 out: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """logits = lm_head(rmsnorm(hidden) * norm_weight) (+ bias) as one C-ABI operator (vb_norm_lmhead; orpheus.py:193-197,
@@ -926,16 +937,35 @@ def _dt(x) -> int:
 
 
 def embed_rows_f32(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, pos_table: Optional[torch.Tensor] = None,
-                   pos: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out [T, W] fp32 = table[ids] (+ pos_table[pos]: learned positions); tables bf16 or fp32, of one type."""
+                   pos: Optional[torch.Tensor] = None, scale: float = 1.0, out2: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out [T, W] fp32 = table[ids] * scale (+ pos_table[pos]: learned positions); tables bf16 or fp32, of one type.
+    out2 (fp32, like out): a second copy of the rows."""
     _need_cuda(table, ids, out)
     assert ids.dtype == torch.int32 and out.dtype == F32 and table.is_contiguous() and out.is_contiguous()
     if pos_table is not None:
         assert pos_table.dtype == table.dtype and pos_table.is_contiguous() and pos_table.shape[1] == table.shape[1]
         assert pos.dtype == torch.int32 and pos.numel() >= ids.numel()
     call("vb_embed_rows_f32", out.data_ptr(), table.data_ptr(), ids.data_ptr(), ids.numel(), table.shape[1],
-         table.shape[0], _dt(table), _p(pos_table), _p(pos), pos_table.shape[0] if pos_table is not None else 0, _stream())
+         table.shape[0], _dt(table), _p(pos_table), _p(pos), pos_table.shape[0] if pos_table is not None else 0, float(scale),
+         _p(out2), _stream())
     return out
+
+
+def gated_residual_norm_f32(x: torch.Tensor, y: torch.Tensor, r: Optional[torch.Tensor], bias: Optional[torch.Tensor],
+                            eps: float, out: Optional[torch.Tensor] = None, w: Optional[torch.Tensor] = None,
+                            add: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """In place on the fp32 stream x [T, W]: x += sigmoid(r + bias) * y (r: an fp32 view [T, W] with any row stride; None:
+    x += y); x += add (optional); then out = x / sqrt(mean(x^2) + eps) * w (optional; bf16 or fp32, w fp32 [W])."""
+    _need_cuda(x, y)
+    T, W = x.shape
+    assert x.dtype == F32 and y.dtype == F32 and x.is_contiguous() and y.is_contiguous() and tuple(y.shape) == (T, W)
+    assert r is None or (r.dtype == F32 and r.stride(1) == 1 and tuple(r.shape) == (T, W))
+    assert bias is None or (bias.dtype == F32 and bias.numel() == W)
+    assert add is None or (add.dtype == F32 and add.is_contiguous() and tuple(add.shape) == (T, W))
+    assert out is None or (out.is_contiguous() and w.dtype == F32 and w.numel() == W)
+    call("vb_gated_residual_norm_f32", x.data_ptr(), y.data_ptr(), _p(r), r.stride(0) if r is not None else 0, _p(bias),
+         _p(add), _p(out), _p(w), T, W, float(eps), _dt(out) if out is not None else 1, _stream())
+    return x
 
 
 def rmsnorm2_f32(x: torch.Tensor, w1: torch.Tensor, eps: float, out1: torch.Tensor, w2: Optional[torch.Tensor] = None,
@@ -1010,10 +1040,11 @@ def postnorm_residual_f32(x: torch.Tensor, y: torch.Tensor, w1: torch.Tensor, b1
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0, alpha: float = 1.0,
            row_off: Optional[torch.Tensor] = None, gather: Optional[torch.Tensor] = None,
-           rows: Optional[int] = None) -> torch.Tensor:
+           rows: Optional[int] = None, glu: Optional[Tuple[float, float]] = None) -> torch.Tensor:
     """out [R, N] = alpha * x @ w^T with fp32 accumulation.  x [T, K] and w ([N, K], or [E, N, K] with row_off
     [E + 1] for experts) share a dtype (bf16 or fp32); out bf16 or fp32.  epilogue 1: w holds N gate rows then N up rows
-    (per expert) and out = silu(gate) * up; 2 / 3 / 4: out = relu(y)^2 / gelu(y) (erf) / gelu(y) (tanh form).  gather: int32 source row of x for every output row.  rows: how many rows a
+    (per expert) and out = silu(gate) * up -- with glu = (limit, slope) the clamped form g = min(gate, limit),
+    u = clamp(up, -limit, limit), out = g * sigmoid(slope * g) * (u + 1); 2 / 3 / 4: out = relu(y)^2 / gelu(y) (erf) / gelu(y) (tanh form).  gather: int32 source row of x for every output row.  rows: how many rows a
     group can have at most (grouped) / how many rows to compute (dense); default x.shape[0]."""
     _need_cuda(x, w, out)
     assert x.dtype == w.dtype and x.stride(-1) == 1 and w.is_contiguous() and out.stride(-1) == 1
@@ -1023,7 +1054,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 
     assert x.shape[1] == K and out.shape[1] >= N
     T = x.shape[0] if rows is None else rows
     call("vb_linear", out.data_ptr(), x.data_ptr(), w.data_ptr(), T, N, K, x.stride(0), out.stride(0), _dt(x), _dt(out),
-         epilogue, float(alpha), _p(row_off), _p(gather), groups, n_rows_w * K, _stream())
+         epilogue, float(alpha), _p(row_off), _p(gather), groups, n_rows_w * K, float(glu[0]) if glu else 0.0,
+         float(glu[1]) if glu else 0.0, _stream())
     return out
 
 
@@ -1033,16 +1065,18 @@ LINEAR_ACTS = {None: 0, "relu2": 2, "gelu": 3, "gelu_tanh": 4}
 def linear_batched(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None,
                    alpha: float = 1.0, epilogue: int = 0) -> torch.Tensor:
     """out[t, g, :] = alpha * w[g] @ x[t, g, :] for every group g (the heads of a token side by side): x [T, G, K],
-    w [G, N, K] (one dtype, bf16 or fp32), out [T, G, N] (bf16 or fp32), fp32 accumulation in k order.  gate: an fp32 view
+    w [G, N, K] (one dtype, bf16 or fp32), out [T, G, N] (bf16 or fp32), fp32 accumulation in k order.  x and out may be
+    views whose last axis is dense (a leading slice of every head of a wider tensor).  gate: an fp32 view
     [T, >= G] (any row stride); out[t, g, :] is multiplied by sigmoid(gate[t, g])."""
     _need_cuda(x, w, out)
     T, G, K = x.shape
     N = w.shape[1]
-    assert x.dtype == w.dtype and x.is_contiguous() and w.is_contiguous() and out.is_contiguous()
+    assert x.dtype == w.dtype and x.stride(2) == 1 and w.is_contiguous() and out.stride(2) == 1
     assert tuple(w.shape) == (G, N, K) and tuple(out.shape) == (T, G, N)
     assert gate is None or (gate.dtype == F32 and gate.stride(1) == 1 and gate.shape[1] >= G)
-    call("vb_linear_batched", out.data_ptr(), x.data_ptr(), w.data_ptr(), T, N, K, G * K, G * N, K, N, N * K, G, _dt(x),
-         _dt(out), epilogue, float(alpha), _p(gate), gate.stride(0) if gate is not None else 0, _stream())
+    call("vb_linear_batched", out.data_ptr(), x.data_ptr(), w.data_ptr(), T, N, K, x.stride(0), out.stride(0), x.stride(1),
+         out.stride(1), N * K, G, _dt(x), _dt(out), epilogue, float(alpha), _p(gate),
+         gate.stride(0) if gate is not None else 0, _stream())
     return out
 
 
@@ -1075,11 +1109,90 @@ def sum_planes_f32(partials: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def rotary_table(pos: torch.Tensor, freq: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out [T, 2, half] fp32 = cos | sin of pos[t] * freq[j]; freq float64 [half]."""
+def rotary_table(pos: torch.Tensor, freq: torch.Tensor, out: torch.Tensor, mult: float = 1.0) -> torch.Tensor:
+    """out [T, 2, half] fp32 = mult * (cos | sin) of pos[t] * freq[j]; freq float64 [half]."""
     _need_cuda(pos, freq, out)
     assert pos.dtype == torch.int32 and freq.dtype == torch.float64 and out.dtype == F32
-    call("vb_rotary_table", out.data_ptr(), pos.data_ptr(), freq.data_ptr(), pos.numel(), freq.numel(), _stream())
+    call("vb_rotary_table", out.data_ptr(), pos.data_ptr(), freq.data_ptr(), pos.numel(), freq.numel(), float(mult), _stream())
+    return out
+
+
+ROTARY_LAYOUTS = {"interleaved": 0, "half": 1}
+
+
+def qkv_norm_rotary_append(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, cs: Optional[torch.Tensor], half: int,
+                           layout: str, q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float,
+                           q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, row_req: torch.Tensor,
+                           pos: torch.Tensor, page_indptr: torch.Tensor, page_indices: torch.Tensor, T: int, Hq: int) -> None:
+    """proj fp32 [T, ld]: Hq query heads and the key heads of k_cache [pages, page, Gk, dim] are RMS-normed over dim (weights
+    fp32 [dim] shared by all heads, None: no norm), rotated on their first 2 * half dims in the given layout and written to
+    q_out / appended; the values are appended to v_cache [pages, page, Gv, vdim] as they are."""
+    _need_cuda(proj, q_out, k_cache, v_cache)
+    assert proj.dtype == F32 and proj.stride(1) == 1 and k_cache.dtype == q_out.dtype == v_cache.dtype
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.shape[1] == v_cache.shape[1]
+    Gk, dim, Gv, vdim = k_cache.shape[2], k_cache.shape[3], v_cache.shape[2], v_cache.shape[3]
+    for w in (q_norm, k_norm):
+        assert w is None or (w.dtype == F32 and w.numel() == dim)
+    call("vb_qkv_norm_rotary_append", proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, _p(cs), half,
+         ROTARY_LAYOUTS[layout], _p(q_norm), _p(k_norm), float(eps), q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+         row_req.data_ptr(), pos.data_ptr(), page_indptr.data_ptr(), page_indices.data_ptr(), k_cache.shape[1], T, Hq, Gk, Gv,
+         dim, vdim, _dt(q_out), _stream())
+
+
+def latent_rope_append(proj: torch.Tensor, q_off: int, c_off: int, H: int, dim: int, rot: int, kv_rank: int, wc: torch.Tensor,
+                       cs: Optional[torch.Tensor], half: int, layout: str, q_out: torch.Tensor, q_lat: torch.Tensor,
+                       cache: torch.Tensor, row_req: torch.Tensor, pos: torch.Tensor, page_indptr: torch.Tensor,
+                       page_indices: torch.Tensor, T: int, eps: float) -> None:
+    """proj fp32 [T, ld] holds H query heads of dim + rot values at q_off and the key/value latent (kv_rank) followed by the
+    shared rotated key part (rot) at c_off.  The latent is RMS-normed (wc) and appended with the rotated key part to cache
+    [pages, page, 1, kv_rank + rot]; the queries' unrotated parts go to q_out [T, H, dim], their rotated parts to
+    q_lat[:, :, kv_rank:] (q_lat [T, H, kv_rank + rot])."""
+    _need_cuda(proj, q_out, q_lat, cache)
+    assert proj.dtype == F32 and proj.stride(1) == 1 and wc.dtype == F32 and wc.numel() == kv_rank
+    assert cache.dtype == q_out.dtype == q_lat.dtype and cache.is_contiguous() and q_out.is_contiguous() and q_lat.is_contiguous()
+    assert cache.shape[-1] == kv_rank + rot and q_lat.shape[-1] == kv_rank + rot
+    call("vb_latent_rope_append", proj.data_ptr(), proj.stride(0), q_off, c_off, H, dim, rot, kv_rank, wc.data_ptr(), _p(cs),
+         half, ROTARY_LAYOUTS[layout], q_out.data_ptr(), q_lat.data_ptr(), cache.data_ptr(), row_req.data_ptr(), pos.data_ptr(),
+         page_indptr.data_ptr(), page_indices.data_ptr(), cache.shape[1], T, float(eps), _dt(q_out), _stream())
+
+
+def head_pair_combine(a: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor], H: int, R: int, vdim: int, lam: float,
+                      post: float, eps: float) -> torch.Tensor:
+    """a fp32 [T, 2H * vdim], per group of R heads [first map of the R heads | second map]: o = a1 - lam * a2 per head,
+    o / sqrt(mean(o^2) + eps) * post * sigmoid(gate) -> out [T, H * vdim] (bf16 or fp32); gate: fp32 view [T, H * vdim]."""
+    _need_cuda(a, out)
+    T = out.shape[0]
+    assert a.dtype == F32 and a.is_contiguous() and out.is_contiguous() and a.shape[1] == 2 * H * vdim and out.shape[1] == H * vdim
+    assert gate is None or (gate.dtype == F32 and gate.stride(1) == 1)
+    call("vb_head_pair_combine", out.data_ptr(), a.data_ptr(), _p(gate), gate.stride(0) if gate is not None else 0, T, H, R,
+         vdim, float(lam), float(post), float(eps), _dt(out), _stream())
+    return out
+
+
+def mingru(proj: torch.Tensor, z_off: int, x_off: int, g_off: int, bz: Optional[torch.Tensor], bx: Optional[torch.Tensor],
+           state: torch.Tensor, out: torch.Tensor, qo_indptr: torch.Tensor, pos: torch.Tensor, slots: torch.Tensor, B: int,
+           single_rows: bool = True, multi_rows: bool = True) -> torch.Tensor:
+    """minGRU over the fp32 projection rows (see vb_api.h); state fp32 [slots, width]; out [T, width] bf16 or fp32."""
+    _need_cuda(proj, state, out)
+    assert proj.dtype == F32 and proj.stride(1) == 1 and state.dtype == F32 and state.is_contiguous() and out.is_contiguous()
+    width = state.shape[1]
+    assert out.shape[1] == width and all(b is None or (b.dtype == F32 and b.numel() == width) for b in (bz, bx))
+    call("vb_mingru", out.data_ptr(), state.data_ptr(), proj.data_ptr(), proj.stride(0), z_off, x_off, g_off, _p(bz), _p(bx),
+         qo_indptr.data_ptr(), pos.data_ptr(), slots.data_ptr(), B, width, int(single_rows), int(multi_rows), _dt(out), _stream())
+    return out
+
+
+def mingru_tiled(proj: torch.Tensor, z_off: int, x_off: int, g_off: int, bz: Optional[torch.Tensor],
+                 bx: Optional[torch.Tensor], state: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor,
+                 qo_indptr: torch.Tensor, pos: torch.Tensor, slots: torch.Tensor, tile_req: torch.Tensor,
+                 tile_row0: torch.Tensor, n_tiles: int, tile_rows: int, B: int) -> torch.Tensor:
+    """Prompt portions with their tiles processed in parallel (requests that bring one row are not touched)."""
+    _need_cuda(proj, state, out, scratch)
+    width = state.shape[1]
+    assert proj.dtype == F32 and state.dtype == F32 and scratch.dtype == F32 and scratch.numel() >= n_tiles * 2 * width
+    call("vb_mingru_tiled", out.data_ptr(), state.data_ptr(), scratch.data_ptr(), proj.data_ptr(), proj.stride(0), z_off, x_off,
+         g_off, _p(bz), _p(bx), qo_indptr.data_ptr(), pos.data_ptr(), slots.data_ptr(), tile_req.data_ptr(),
+         tile_row0.data_ptr(), n_tiles, tile_rows, B, width, _dt(out), _stream())
     return out
 
 
@@ -1101,26 +1214,31 @@ def window_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, o
                 page_indices: torch.Tensor, T: int, H: int, G: int, dim: int, vdim: int, window: int, scale: float,
                 tiles: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor, int]] = None,
                 scratch: Optional[torch.Tensor] = None, rows: Optional[Tuple[torch.Tensor, int]] = None,
-                head_rows: bool = False) -> torch.Tensor:
+                head_rows: bool = False, chunk: int = 0, k_ld: int = 0, v_ld: int = 0, v_share: int = 1) -> torch.Tensor:
     """gate: an fp32 view [T, H * vdim] (any row stride) or None.  tiles = (qo_indptr, tile_req, tile_row0, n_tiles):
     run the tiled prompt kernel over those row tiles instead of the per-row kernel.  scratch (fp32): lets the per-row kernel
     split a row's keys over several CTAs when the step has few rows.  rows = (int32 row indices, count): serve only those
     rows (per-row kernel).  head_rows: where sizes allow, single-token rows run as tensor-core tiles whose rows are the query
-    heads that share a key/value head (many heads on few key/value heads: latent attention)."""
+    heads that share a key/value head (many heads on few key/value heads: latent attention).  chunk > 0: a position sees
+    only the keys of its own block of `chunk` positions.  k_ld / v_ld: elements per token of the key / value cache when they
+    are not G * dim / G * vdim (values that are a leading slice of the key rows).  v_share: consecutive key heads reading one
+    value head.  An fp32 ``out`` beside bf16 operands is written in fp32."""
     _need_cuda(q, k_cache, v_cache, out)
+    out_f32 = int(out.dtype == F32)
     ld_gate = gate.stride(0) if gate is not None else 0
     if tiles is None:
         n = T if rows is None else rows[1]
         call("vb_window_attn", out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _p(gate), ld_gate,
              row_req.data_ptr(), pos.data_ptr(), page_indptr.data_ptr(), page_indices.data_ptr(), n, H, G, dim, vdim,
              k_cache.shape[1], int(window), float(scale), _dt(q), _p(scratch), scratch.numel() if scratch is not None else 0,
-             _p(rows[0]) if rows is not None else None, int(head_rows), _stream())
+             _p(rows[0]) if rows is not None else None, int(head_rows), int(chunk), int(k_ld), int(v_ld), int(v_share), out_f32,
+             _stream())
     else:
         qo, tile_req, tile_row0, n_tiles = tiles
         call("vb_window_attn_tiled", out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _p(gate),
              ld_gate, pos.data_ptr(), page_indptr.data_ptr(), page_indices.data_ptr(), qo.data_ptr(), tile_req.data_ptr(),
              tile_row0.data_ptr(), n_tiles, T, H, G, dim, vdim, k_cache.shape[1], int(window), float(scale), _dt(q),
-             _stream())
+             int(chunk), int(k_ld), int(v_ld), int(v_share), out_f32, _stream())
     return out
 
 
