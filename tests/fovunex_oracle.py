@@ -212,3 +212,88 @@ def greedy(cfg, sd, prompt, n_new: int) -> List[int]:
     for _ in range(n_new):
         toks.append(int(forward(cfg, sd, toks)[0][-1].argmax()))
     return toks[len(prompt):]
+
+
+# ---- small configurations and random weights for the tests ----------------------------------------------------------------
+def make_config(width=40, vocab=53, layers=("latent", "gru", "attention", "latent"), loop=(1, 3, 2), eps=1e-5, embed_scale=2.0,
+                heads=3, dim=8, rot_dim=6, vdim=10, kv_rank=12, lat_scale=0.27, yarn=(4.0, 64, 8.0, 1.0), lat_base=500.0,
+                a_heads=4, a_kv_heads=2, a_dim=12, a_vdim=6, a_scale=0.29, diff=0.4, chunk=9, a_rot=(8, 3000.0),
+                gru_width=28, ff=24, limit=1.2) -> Dict[str, Any]:
+    """layers: "latent" / "attention" / "gru" (each with a feed-forward), the same with "-" appended (no feed-forward), or a
+    dictionary {"kind": ..., "ff": n or None, **overrides of the mixer's sizes}.  yarn = (factor, original, fast, slow) or
+    None; a_rot = (dims, base) or None; loop = (start, stop, times) or None."""
+    out = []
+    for spec in layers:
+        spec = {"kind": spec} if isinstance(spec, str) else dict(spec)
+        kind = spec.pop("kind")
+        has_ff = not kind.endswith("-")
+        kind = kind.rstrip("-")
+        f = spec.pop("ff", ff if has_ff else None)
+        lim = spec.pop("limit", limit)
+        if kind == "latent":
+            m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "scale": lat_scale}
+            m.update(spec)
+            if m["rot_dim"] and "rot" not in m:
+                m["rot"] = {"base": lat_base, "dims": m["rot_dim"]}
+                if yarn:
+                    m["rot"]["scaling"] = dict(zip(("factor", "original", "fast", "slow"), yarn))
+            t = "latent_attention"
+        elif kind == "attention":
+            m = {"heads": a_heads, "kv_heads": a_kv_heads, "dim": a_dim, "vdim": a_vdim, "scale": a_scale, "diff": diff}
+            if chunk:
+                m["mask"] = {"size": chunk}
+            if a_rot:
+                m["rot"] = {"dims": a_rot[0], "base": a_rot[1]}
+            m.update(spec)
+            t = "attention"
+        else:
+            m = {"width": gru_width}
+            m.update(spec)
+            t = "mingru"
+        out.append({"type": t, "mixer": m, "mlp": {"kind": "dense", "ff": f, "limit": lim} if f else None})
+    cfg = {"architecture": "Fovunex", "width": width, "vocab": vocab, "norm": {"eps": eps}, "embedding": {"scale": embed_scale},
+           "layers": out}
+    if loop:
+        cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return cfg
+
+
+def random_weights(cfg: Dict[str, Any], seed: int = 0, head_gain: float = 1.0) -> Dict[str, torch.Tensor]:
+    """bfloat16 tensors under the checkpoint's names."""
+    g = torch.Generator().manual_seed(seed)
+    W = cfg["width"]
+
+    def rnd(*shape, std=1.0, mean=0.0):
+        return (torch.randn(tuple(shape), generator=g) * std + mean).to(torch.bfloat16)
+
+    sd = {"embed": rnd(cfg["vocab"], W), "head": rnd(cfg["vocab"], W, std=head_gain * W ** -0.5), "final.norm": rnd(std=0.1, mean=1.2)}
+    s = W ** -0.5
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        sd[p + "norm1"], sd[p + "rg1"], sd[p + "rg1.b"] = rnd(std=0.2, mean=1.0), rnd(W, W, std=2 * s), rnd(W, std=0.7)
+        if L["type"] == "latent_attention":
+            H, D, Rd, V, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            sd[p + "mix.q"], sd[p + "mix.dkv"] = rnd(H * (D + Rd), W, std=3 * s), rnd(R + Rd, W, std=3 * s)
+            sd[p + "mix.dkv.norm"] = rnd(R, std=0.2, mean=1.0)
+            sd[p + "mix.uk"], sd[p + "mix.uv"] = rnd(H * D, R, std=2 * R ** -0.5), rnd(H * V, R, std=R ** -0.5)
+            sd[p + "mix.o"] = rnd(W, H * V, std=2 * (H * V) ** -0.5)
+        elif L["type"] == "attention":
+            H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            sd[p + "mix.q"], sd[p + "mix.k"] = rnd(H * 2 * D, W, std=s), rnd(G * 2 * D, W, std=s)
+            sd[p + "mix.v"], sd[p + "mix.g"] = rnd(G * V, W, std=s), rnd(H * V, W, std=2 * s)
+            sd[p + "mix.q.norm"], sd[p + "mix.k.norm"] = rnd(D, std=0.4, mean=1.5), rnd(D, std=0.4, mean=1.5)
+            for n in ("lq1", "lk1", "lq2", "lk2"):
+                sd[p + "mix." + n] = rnd(D, std=0.25)
+            sd[p + "mix.o"] = rnd(W, H * V, std=2 * (H * V) ** -0.5)
+        else:
+            Wm = m["width"]
+            for n in ("z", "x", "g"):
+                sd[p + "mix." + n] = rnd(Wm, W, std=2 * s)
+            sd[p + "mix.z.b"], sd[p + "mix.x.b"] = rnd(Wm, std=0.7), rnd(Wm, std=0.7)
+            sd[p + "mix.o"] = rnd(W, Wm, std=2 * Wm ** -0.5)
+        f = L["mlp"]
+        if f:
+            sd[p + "norm2"], sd[p + "rg2"], sd[p + "rg2.b"] = rnd(std=0.2, mean=1.0), rnd(W, W, std=2 * s), rnd(W, std=0.7)
+            sd[p + "mlp.gate"], sd[p + "mlp.up"] = rnd(f["ff"], W, std=2 * s), rnd(f["ff"], W, std=2 * s)
+            sd[p + "mlp.down"] = rnd(W, f["ff"], std=2 * f["ff"] ** -0.5)
+    return sd
