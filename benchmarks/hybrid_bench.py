@@ -8,6 +8,10 @@ uses (top * ff + shared ff).  Random weights, a few layers of a real model's sha
 closest relative on the same engine, Bobavik with softmax-attention layers only, at equal width, heads, head size and
 expert sizes.
 
+``--arch fovunex``: the Fovunex design (gated pre-norm blocks; latent attention with a shared rotated key part, attention with
+two score maps per head in chunks, minGRU, clamped gated dense feed-forward) beside Bobavik (softmax attention and linear
+attention with a recurrent state, mixture of experts) at equal width, head count and feed-forward width per token.
+
 Per size and engine: prefill of one 1024-token prompt (eager launches) and one decode step of 32 requests at context 512
 (a CUDA-graph replay, as served), timed with CUDA events after warm-up; an L2-sized buffer is overwritten between timed
 iterations.  Output: one JSON line per size.
@@ -36,6 +40,25 @@ def razevik_config(width: int, ff: int, experts: int = 8, top: int = 2) -> dict:
         layers.append({"type": "latent_attention", "mixer": m, "mlp": {"kind": "dense", "ff": 3 * ff} if i == 0 else dict(moe)})
     return {"architecture": "Razevik", "width": width, "vocab": VOCAB, "max_positions": 2048, "norm": {"eps": 1e-6},
             "residual_mult": 0.5, "token_side": {"dim": 32}, "logit_softcap": 30.0, "layers": layers}
+
+
+def fovunex_config(width: int, ff: int) -> dict:
+    """four layers: latent attention + feed-forward, minGRU, two-map attention + feed-forward, latent attention + feed-forward;
+    128-wide heads (latent attention: 128 unrotated + 64 rotated dims on a latent of 128; two-map attention: two maps of 64
+    dims on 128-wide values, a quarter as many key/value heads), chunks of 4096 positions, a dense feed-forward as wide as the
+    experts a Bobavik token uses"""
+    heads = width // 128
+    lat = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 128, "scale": 192 ** -0.5,
+           "rot": {"base": 1e4, "dims": 64, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    att = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "diff": 0.5,
+           "mask": {"size": 4096}, "rot": {"dims": 64, "base": 1e6}}
+    mlp = {"kind": "dense", "ff": 3 * ff, "limit": 7.0}
+    layers = [{"type": "latent_attention", "mixer": dict(lat), "mlp": dict(mlp)},
+              {"type": "mingru", "mixer": {"width": width}, "mlp": None},
+              {"type": "attention", "mixer": dict(att), "mlp": dict(mlp)},
+              {"type": "latent_attention", "mixer": dict(lat), "mlp": dict(mlp)}]
+    return {"architecture": "Fovunex", "width": width, "vocab": VOCAB, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "layers": layers}
 
 
 def bobavik_config(width: int, ff: int, experts: int = 8, top: int = 2, window: int = 4096,
@@ -84,9 +107,12 @@ def bench_bobavik(width: int, ff: int, steps: int, warmup: int, flush, kinds=Non
     from vox_serve_b200 import ops
     from vox_serve_b200.hybrid_engine import StepInputs
     from vox_serve_b200.model.bobavik import BobavikModel
+    from vox_serve_b200.model.fovunex import FovunexModel
     from vox_serve_b200.model.razevik import RazevikModel
 
-    if design == "razevik":
+    if design == "fovunex":
+        model = FovunexModel("fovunex-synthetic:1", config=fovunex_config(width, ff), device="cuda:0")
+    elif design == "razevik":
         model = RazevikModel("razevik-synthetic:1", config=razevik_config(width, ff), device="cuda:0")
     else:
         cfg = bobavik_config(width, ff, **({"kinds": kinds} if kinds else {}))
@@ -177,6 +203,17 @@ def run(sizes, steps: int, warmup: int, only: str = "", arch: str = "bobavik") -
     flush = torch.zeros(192 << 20, dtype=torch.uint8, device="cuda")
     for width in sizes:
         ff = width                     # expert width; a token uses top (2) experts + the shared one
+        if arch == "fovunex":
+            line = {"bench": "fovunex_vs_bobavik", "width": width, "layers": LAYERS, "prompt": PROMPT, "decode_batch": BATCH,
+                    "context": CONTEXT, "steps": steps, "warmup": warmup, "dtype": "bf16", "data": "synthetic",
+                    "l2": "192 MiB buffer overwritten between timed iterations"}
+            if only in ("", "fovunex"):
+                line["fovunex"] = bench_bobavik(width, ff, steps, warmup, flush, design="fovunex")
+            if only in ("", "bobavik"):
+                line["bobavik"] = bench_bobavik(width, ff, steps, warmup, flush)
+            print(json.dumps(line), flush=True)
+            torch.cuda.empty_cache()
+            continue
         if arch == "razevik":
             line = {"bench": "razevik_vs_bobavik_attention", "width": width, "layers": LAYERS, "prompt": PROMPT,
                     "decode_batch": BATCH, "context": CONTEXT, "steps": steps, "warmup": warmup, "dtype": "bf16",

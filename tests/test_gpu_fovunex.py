@@ -406,13 +406,16 @@ def _latent_rot_case(T, page_size, hot, dtype, mode, H=3, D=8, Rd=4, V=4, R=12):
 @pytest.mark.parametrize("dtype", [F32, BF16])
 def test_latent_attention_with_rotated_part_far_keys_and_page_borders(mode, dtype):
     tol = 2e-3 if dtype == F32 else 4e-2
-    sizes = dict(H=3, D=8, Rd=4, V=4, R=12) if dtype == F32 else dict(H=2, D=16, Rd=16, V=16, R=32)
-    for hot, T, ps in ((0, 40, 8), (7, 300, 8), (8, 130, 8), (63, 200, 64), (64, 131, 64), (5, 70, 16)):
-        got, ref = _latent_rot_case(T, ps, hot, dtype, mode, **sizes)
-        assert torch.allclose(got.double(), ref, rtol=tol, atol=tol * 10), (hot, T, ps)
-        sees = got[:, 0, 0] > 500
-        for i in range(T):
-            assert bool(sees[i]) == (i >= hot), (hot, i)
+    # (bfloat16: rows of 48 and of 192 dims, the two widths of the tensor-core tile kernel's query fragments)
+    all_sizes = [dict(H=3, D=8, Rd=4, V=4, R=12)] if dtype == F32 else [dict(H=2, D=16, Rd=16, V=16, R=32),
+                                                                         dict(H=3, D=16, Rd=64, V=16, R=128)]
+    for sizes in all_sizes:
+        for hot, T, ps in ((0, 40, 8), (7, 300, 8), (8, 130, 8), (63, 200, 64), (64, 131, 64), (5, 70, 16)):
+            got, ref = _latent_rot_case(T, ps, hot, dtype, mode, **sizes)
+            assert torch.allclose(got.double(), ref, rtol=tol, atol=tol * 10), (hot, T, ps)
+            sees = got[:, 0, 0] > 500
+            for i in range(T):
+                assert bool(sees[i]) == (i >= hot), (hot, i)
 
 
 # ---- the other mechanisms alone ----------------------------------------------------------------------------------------

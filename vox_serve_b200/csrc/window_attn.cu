@@ -724,8 +724,10 @@ __global__ void __launch_bounds__(64) window_attn_merge_kernel(WindowAttnParams 
 // memory as bf16 with 16-byte loads; S = Q K^T and O += P V run as mma.sync m16n8k16 with fp32 accumulators, the softmax
 // (scale, window mask, running max and sum) in fp32 on the accumulator fragments, P rounded to bf16 for the second product.
 // ------------------------------------------------------------------------------------------------------------------
-constexpr int FM = 64, FN = 64, F_KB = 8, F_NT = 16;      // dim <= 16 * F_KB, vdim <= 8 * F_NT
+constexpr int FM = 64, FN = 64, F_KB = 12, F_NT = 16;      // dim <= 16 * F_KB, vdim <= 8 * F_NT
+// (KB: the query fragments a thread holds, 16 key dims each; 8 for heads up to 128 dims, 12 up to 192)
 
+template <int KB>
 __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnParams p) {
   extern __shared__ __align__(16) uint8_t smraw[];
   pdl_sync();
@@ -760,9 +762,9 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnParams p
     *reinterpret_cast<uint4*>(Ks + r * ldk + c) = v;
   }
   __syncthreads();
-  uint32_t qf[F_KB][4];
+  uint32_t qf[KB][4];
 #pragma unroll
-  for (int kb = 0; kb < F_KB; ++kb)
+  for (int kb = 0; kb < KB; ++kb)
     if (kb < nkb) ldmatrix_x4(qf[kb], smem_u32(Ks + (warp * 16 + (lane & 15)) * ldk + kb * 16 + (lane >> 4) * 8));
   const int pos_last = pos0 + (nrows - 1) * pstep;
   const int rA = warp * 16 + (lane >> 2), rB = rA + 8;
@@ -829,7 +831,7 @@ __global__ void __launch_bounds__(128) window_attn_mma_kernel(WindowAttnParams p
 #pragma unroll
     for (int n = 0; n < FN / 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
 #pragma unroll
-    for (int kb = 0; kb < F_KB; ++kb) {
+    for (int kb = 0; kb < KB; ++kb) {
       if (kb < nkb) {
 #pragma unroll
         for (int np = 0; np < FN / 16; ++np) {
@@ -1075,8 +1077,13 @@ int vb_window_attn(void* d_out, const void* d_q, const void* d_k_cache, const vo
     p.row_heads = 1;
     p.splits = splits;
     const size_t msmem = 2 * static_cast<size_t>(FN) * (dim + 8 + vdim + 8) * sizeof(__nv_bfloat16);
-    VB_CHECK_CUDA(cudaFuncSetAttribute(window_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
-    VB_LAUNCH_PDL(window_attn_mma_kernel, dim3(T, G, splits), 128, msmem, stream, p);
+    if (dim <= 128) {
+      VB_CHECK_CUDA(cudaFuncSetAttribute(window_attn_mma_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+      VB_LAUNCH_PDL(window_attn_mma_kernel<8>, dim3(T, G, splits), 128, msmem, stream, p);
+    } else {
+      VB_CHECK_CUDA(cudaFuncSetAttribute(window_attn_mma_kernel<F_KB>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+      VB_LAUNCH_PDL(window_attn_mma_kernel<F_KB>, dim3(T, G, splits), 128, msmem, stream, p);
+    }
     if (splits > 1) VB_LAUNCH_PDL(window_attn_merge_kernel<bf16>, dim3(T, H), 64, 0, stream, p);
     return 0;
   }
@@ -1135,8 +1142,13 @@ int vb_window_attn_tiled(void* d_out, const void* d_q, const void* d_k_cache, co
   dim3 grid(n_tiles, H);
   if (dtype == 0 && dim % 16 == 0 && vdim % 16 == 0 && dim <= 16 * F_KB && vdim <= 8 * F_NT && k_ld % 8 == 0 && v_ld % 8 == 0) {
     const size_t msmem = 2 * static_cast<size_t>(FN) * (dim + 8 + vdim + 8) * sizeof(__nv_bfloat16);      // two stages
-    VB_CHECK_CUDA(cudaFuncSetAttribute(window_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
-    VB_LAUNCH_PDL(window_attn_mma_kernel, grid, 128, msmem, stream, p);
+    if (dim <= 128) {
+      VB_CHECK_CUDA(cudaFuncSetAttribute(window_attn_mma_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+      VB_LAUNCH_PDL(window_attn_mma_kernel<8>, grid, 128, msmem, stream, p);
+    } else {
+      VB_CHECK_CUDA(cudaFuncSetAttribute(window_attn_mma_kernel<F_KB>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+      VB_LAUNCH_PDL(window_attn_mma_kernel<F_KB>, grid, 128, msmem, stream, p);
+    }
     return 0;
   }
   const size_t smem = (static_cast<size_t>(WT_ROWS + WT_KEYS) * (dim + 1) + static_cast<size_t>(WT_KEYS) * (vdim + 1) +
