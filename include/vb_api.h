@@ -603,8 +603,9 @@ int vb_window_attn_tiled(void* d_out, const void* d_q, const void* d_k_cache, co
  * c = u + 1/2 (u >= 0) or sigmoid(u), S_t = (1 - z) S_(t-1) + z c (S = 0 before position 0), out = S_t * silu(pg); pz, px,
  * pg are columns z_off, x_off, g_off of the fp32 projection rows.  single_rows / multi_rows select the requests served.
  * vb_mingru_tiled: prompt portions as tiles of tile_rows rows (tile i = rows tile_row0[i].. of request tile_req[i], in
- * request order; single-row requests have none): tile summaries, a scan over each request's tiles, outputs per tile;
- * d_scratch fp32 [n_tiles][2][width] */
+ * request order; single-row requests have none), each cut into pieces of 16 rows: piece summaries, a scan over each
+ * request's pieces, outputs per piece; d_scratch: vb_mingru_scratch_floats(n_tiles, tile_rows, width) floats; tile_rows a
+ * multiple of 16 */
 int vb_mingru(void* d_out, float* d_state, const float* d_proj, int ldp, int z_off, int x_off, int g_off, const float* d_bz,
               const float* d_bx, const int32_t* d_qo_indptr, const int32_t* d_pos, const int32_t* d_slots, int B, int width,
               int single_rows, int multi_rows, int out_dtype, void* stream);
@@ -612,6 +613,7 @@ int vb_mingru_tiled(void* d_out, float* d_state, float* d_scratch, const float* 
                     int g_off, const float* d_bz, const float* d_bx, const int32_t* d_qo_indptr, const int32_t* d_pos,
                     const int32_t* d_slots, const int32_t* d_tile_req, const int32_t* d_tile_row0, int n_tiles, int tile_rows,
                     int B, int width, int out_dtype, void* stream);
+int vb_mingru_scratch_floats(int n_tiles, int tile_rows, int width);
 /* Linear attention with a scalar decay per head; q, k, v = silu of the projection columns; state fp32
  * [slots][H][dim][vdim], zero for a request whose first new token has position 0.  single_rows / multi_rows select
  * the step kernel (requests bringing one token) and the chunked kernel (requests bringing more). */

@@ -547,7 +547,7 @@ def test_mingru_state_slots_tiles_and_portions():
                 multi = any(qo[i + 1] - qo[i] > 1 for i in range(len(slots)))
                 single = any(qo[i + 1] - qo[i] == 1 for i in range(len(slots)))
                 if par and tile_req:
-                    scratch = torch.full((len(tile_req) * 2 * Wm,), float("nan"), dtype=F32, device=DEV)
+                    scratch = torch.full((ops.mingru_scratch_floats(len(tile_req), tile, Wm),), float("nan"), dtype=F32, device=DEV)
                     if single:
                         ops.mingru(proj.to(DEV), 2, 2 + Wm, 4 + 2 * Wm, sd["z.b"].to(DEV), sd["x.b"].to(DEV), st, out, dev(qo), dev(pos),
                                    dev(slots), len(slots), single_rows=True, multi_rows=False)
@@ -578,7 +578,7 @@ def test_gated_residual_norm_embedding_scale_and_clamped_feed_forward(W, T):
     g = torch.Generator().manual_seed(W)
     eps = 1e-5
     x, y, add = (torch.randn(T, W, generator=g) for _ in range(3))
-    r = torch.randn(T, W + 9, generator=g)
+    r = torch.randn(T, W + 12, generator=g)
     bias, nw = torch.randn(W, generator=g), torch.full((W,), 1.3)
     for use_add, use_gate, dt in ((True, True, F32), (False, True, BF16), (True, False, F32), (False, False, F32)):
         xd = x.clone().to(DEV)

@@ -129,6 +129,7 @@ SIGNATURES = {
     "vb_mingru": (c_int, [P, P, P, c_int, c_int, c_int, c_int, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P]),
     "vb_mingru_tiled": (c_int, [P, P, P, P, c_int, c_int, c_int, c_int, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int,
                                 c_int, P]),
+    "vb_mingru_scratch_floats": (c_int, [c_int, c_int, c_int]),
     "vb_gemm_bf16_glu": (c_int, [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, P]),
     "vb_qkv_rotary_append": (c_int, [P, c_int, c_int, c_int, c_int, P, c_int, P, P, P, P, P, P, P, c_int, c_int, c_int,
                                      c_int, c_int, c_int, c_int, P, P, c_int, P]),
@@ -211,7 +212,7 @@ def check(rc: int, what: str = ""):
 # kernels (+ memset nodes) each entry point enqueues; everything not listed launches exactly one
 LAUNCHES = {"vb_set_pdl": 0, "vb_set_trace": 0, "vb_weight_tiles_bytes": 0, "vb_tensor_map_kv": 0,
             "vb_tensor_map_2d_bf16": 0, "vb_device_info": 0, "vb_sample": 1, "vb_update_repetition_cache": 1,
-            "vb_set_gemm_smem_kb": 0, "vb_window_attn_tile_rows": 0, "vb_decay_attn_tile_rows": 0, "vb_decay_attn_tiled": 3, "vb_window_attn": 2, "vb_mingru_tiled": 3}
+            "vb_set_gemm_smem_kb": 0, "vb_window_attn_tile_rows": 0, "vb_decay_attn_tile_rows": 0, "vb_decay_attn_tiled": 3, "vb_window_attn": 2, "vb_mingru_tiled": 3, "vb_mingru_scratch_floats": 0}
 launch_counter = [0]
 
 

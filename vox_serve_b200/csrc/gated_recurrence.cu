@@ -10,9 +10,9 @@
 // position 0, so slots are handed out again without clearing.
 //
 //   vb_mingru        one thread per (request, channel) walks the request's rows in order: single-token rows and short portions
-//   vb_mingru_tiled  prompt portions cut into tiles of rows: the recurrence S_t = a_t S_(t-1) + b_t composes as
-//                    (A, B) = (prod a, local end state from zero), so tiles are summarised in parallel, a short scan over a
-//                    request's tiles carries the state in, and the tiles then produce their rows in parallel.
+//   vb_mingru_tiled  prompt portions cut into pieces of rows: the recurrence S_t = a_t S_(t-1) + b_t composes as
+//                    (A, B) = (prod a, local end state from zero), so pieces are summarised in parallel, a short scan over a
+//                    request's pieces carries the state in, and the pieces then produce their rows in parallel.
 #include "../../include/vb_api.h"
 #define VB_PDL_FAMILY 1
 #include "common.cuh"
@@ -35,7 +35,7 @@ struct MinGruParams {
   const int32_t* tile_req;
   const int32_t* tile_row0;
   int n_tiles, tile_rows;
-  float* scratch;         // [n_tiles][2][width]: A, B of every tile; after the scan [..][0] holds the tile's carry-in
+  float* scratch;         // [n_tiles * pieces per tile][2][width]: A, B of every piece; after the scan [..][0] is its carry-in
 };
 
 __device__ __forceinline__ float mg_sigmoid(float v) { return 1.f / (1.f + expf(-v)); }
@@ -73,26 +73,44 @@ __global__ void __launch_bounds__(128) mingru_seq_kernel(MinGruParams p) {
   *st = S;
 }
 
-// tile summaries: A = prod (1 - z_t), B = the tile's end state from a zero start
+// Prompt portions.  A tile (tile_rows rows of one request, as the attention kernels use them) is cut into pieces of MG_ROWS
+// rows; piece j of tile i is summary slot i * pieces_per_tile + j.  A thread owns one channel of one piece and first loads
+// all of the piece's gate inputs (independent loads, all in flight), then runs the short dependent chain over them.
+constexpr int MG_ROWS = 16;
+
+// piece summaries: A = prod (1 - z_t), B = the piece's end state from a zero start
 __global__ void __launch_bounds__(128) mingru_tile_sum_kernel(MinGruParams p) {
   pdl_sync();
-  const int ch = blockIdx.x * 128 + threadIdx.x, tile = blockIdx.y;
+  const int ch = blockIdx.x * 128 + threadIdx.x, ppt = p.tile_rows / MG_ROWS;
+  const int tile = blockIdx.y / ppt, piece = blockIdx.y - tile * ppt;
   if (ch >= p.width) return;
-  const int b = p.tile_req[tile], r0 = p.tile_row0[tile], r1 = min(r0 + p.tile_rows, p.qo_indptr[b + 1]);
+  const int b = p.tile_req[tile], r0 = p.tile_row0[tile] + piece * MG_ROWS;
+  const int n = min(min(r0 + MG_ROWS, p.tile_row0[tile] + p.tile_rows), p.qo_indptr[b + 1]) - r0;
+  float* s = p.scratch + static_cast<size_t>(blockIdx.y) * 2 * p.width;
+  if (n <= 0) { s[ch] = 1.f; s[p.width + ch] = 0.f; return; }
   const float bz = p.bz ? p.bz[ch] : 0.f, bx = p.bx ? p.bx[ch] : 0.f;
-  float A = 1.f, Bv = 0.f;
-  for (int t = r0; t < r1; ++t) {
-    float z, c;
-    mg_gates(p.proj + static_cast<size_t>(t) * p.ldp, p, ch, bz, bx, z, c);
-    A *= 1.f - z;
-    Bv = (1.f - z) * Bv + z * c;
+  float pz[MG_ROWS], px[MG_ROWS];
+#pragma unroll
+  for (int i = 0; i < MG_ROWS; ++i) {
+    const float* row = p.proj + static_cast<size_t>(r0 + min(i, n - 1)) * p.ldp;
+    pz[i] = row[p.z_off + ch];
+    px[i] = row[p.x_off + ch];
   }
-  float* s = p.scratch + static_cast<size_t>(tile) * 2 * p.width;
+  float A = 1.f, Bv = 0.f;
+#pragma unroll
+  for (int i = 0; i < MG_ROWS; ++i) {
+    if (i < n) {
+      const float z = mg_sigmoid(pz[i] + bz), u = px[i] + bx;
+      const float c = u >= 0.f ? u + 0.5f : mg_sigmoid(u);
+      A *= 1.f - z;
+      Bv = (1.f - z) * Bv + z * c;
+    }
+  }
   s[ch] = A;
   s[p.width + ch] = Bv;
 }
 
-// per (request, channel): walk the request's tiles in order, leave every tile's carry-in in scratch[tile][0] and the
+// per (request, channel): walk the request's pieces in order, leave every piece's carry-in in its summary slot [0] and the
 // request's end state in its slot
 __global__ void __launch_bounds__(128) mingru_tile_scan_kernel(MinGruParams p) {
   pdl_sync();
@@ -106,13 +124,29 @@ __global__ void __launch_bounds__(128) mingru_tile_scan_kernel(MinGruParams p) {
     const int mid = (lo + hi) >> 1;
     if (p.tile_req[mid] < b) lo = mid + 1; else hi = mid;
   }
+  int last = lo;
+  while (last < p.n_tiles && p.tile_req[last] == b) ++last;
+  const int ppt = p.tile_rows / MG_ROWS;
   float* st = p.state + static_cast<size_t>(p.slots[b]) * p.width + ch;
   float S = p.pos[r0] == 0 ? 0.f : *st;
-  for (int tile = lo; tile < p.n_tiles && p.tile_req[tile] == b; ++tile) {
-    float* s = p.scratch + static_cast<size_t>(tile) * 2 * p.width;
-    const float A = s[ch], Bv = s[p.width + ch];
-    s[ch] = S;
-    S = A * S + Bv;
+  float* s = p.scratch + static_cast<size_t>(lo) * ppt * 2 * p.width + ch;
+  const int n = (last - lo) * ppt;
+  // (the summaries do not depend on S: eight pieces' loads are issued before their chain runs)
+  for (int i0 = 0; i0 < n; i0 += 8) {
+    float A[8], Bv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const bool ok = i0 + i < n;
+      A[i] = ok ? s[static_cast<size_t>(i0 + i) * 2 * p.width] : 1.f;
+      Bv[i] = ok ? s[static_cast<size_t>(i0 + i) * 2 * p.width + p.width] : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (i0 + i < n) {
+        s[static_cast<size_t>(i0 + i) * 2 * p.width] = S;
+        S = A[i] * S + Bv[i];
+      }
+    }
   }
   *st = S;
 }
@@ -120,18 +154,30 @@ __global__ void __launch_bounds__(128) mingru_tile_scan_kernel(MinGruParams p) {
 template <typename CT>
 __global__ void __launch_bounds__(128) mingru_tile_out_kernel(MinGruParams p) {
   pdl_sync();
-  const int ch = blockIdx.x * 128 + threadIdx.x, tile = blockIdx.y;
+  const int ch = blockIdx.x * 128 + threadIdx.x, ppt = p.tile_rows / MG_ROWS;
+  const int tile = blockIdx.y / ppt, piece = blockIdx.y - tile * ppt;
   if (ch >= p.width) return;
-  const int b = p.tile_req[tile], r0 = p.tile_row0[tile], r1 = min(r0 + p.tile_rows, p.qo_indptr[b + 1]);
+  const int b = p.tile_req[tile], r0 = p.tile_row0[tile] + piece * MG_ROWS;
+  const int n = min(min(r0 + MG_ROWS, p.tile_row0[tile] + p.tile_rows), p.qo_indptr[b + 1]) - r0;
+  if (n <= 0) return;
   const float bz = p.bz ? p.bz[ch] : 0.f, bx = p.bx ? p.bx[ch] : 0.f;
-  float S = p.scratch[static_cast<size_t>(tile) * 2 * p.width + ch];
-  for (int t = r0; t < r1; ++t) {
-    const float* row = p.proj + static_cast<size_t>(t) * p.ldp;
-    float z, c;
-    mg_gates(row, p, ch, bz, bx, z, c);
-    S = (1.f - z) * S + z * c;
-    const float g = row[p.g_off + ch];
-    mg_store<CT>(p.out, static_cast<size_t>(t) * p.width + ch, S * (g * mg_sigmoid(g)));
+  float pz[MG_ROWS], px[MG_ROWS], pg[MG_ROWS];
+#pragma unroll
+  for (int i = 0; i < MG_ROWS; ++i) {
+    const float* row = p.proj + static_cast<size_t>(r0 + min(i, n - 1)) * p.ldp;
+    pz[i] = row[p.z_off + ch];
+    px[i] = row[p.x_off + ch];
+    pg[i] = row[p.g_off + ch];
+  }
+  float S = p.scratch[static_cast<size_t>(blockIdx.y) * 2 * p.width + ch];
+#pragma unroll
+  for (int i = 0; i < MG_ROWS; ++i) {
+    if (i < n) {
+      const float z = mg_sigmoid(pz[i] + bz), u = px[i] + bx;
+      const float c = u >= 0.f ? u + 0.5f : mg_sigmoid(u);
+      S = (1.f - z) * S + z * c;
+      mg_store<CT>(p.out, static_cast<size_t>(r0 + i) * p.width + ch, S * (pg[i] * mg_sigmoid(pg[i])));
+    }
   }
 }
 
@@ -160,16 +206,21 @@ int vb_mingru_tiled(void* d_out, float* d_state, float* d_scratch, const float* 
                     const int32_t* d_slots, const int32_t* d_tile_req, const int32_t* d_tile_row0, int n_tiles, int tile_rows,
                     int B, int width, int out_dtype, void* stream) {
   VB_CHECK_ARG(d_out && d_state && d_scratch && d_proj && d_qo_indptr && d_pos && d_slots && d_tile_req && d_tile_row0 &&
-               width > 0 && tile_rows > 0, "vb_mingru_tiled: bad arguments");
+               width > 0 && tile_rows > 0 && tile_rows % MG_ROWS == 0, "vb_mingru_tiled: bad arguments (tile_rows a multiple of %d)",
+               MG_ROWS);
   if (B <= 0 || n_tiles <= 0) return 0;
   MinGruParams p{d_proj, ldp, z_off, x_off, g_off, d_bz, d_bx, d_state, d_out, d_qo_indptr, d_pos, d_slots, B, width,
                  0, 1, d_tile_req, d_tile_row0, n_tiles, tile_rows, d_scratch};
-  const int cx = (width + 127) / 128;
-  VB_LAUNCH_PDL(mingru_tile_sum_kernel, dim3(cx, n_tiles), 128, 0, stream, p);
+  const int cx = (width + 127) / 128, pieces = n_tiles * (tile_rows / MG_ROWS);
+  VB_LAUNCH_PDL(mingru_tile_sum_kernel, dim3(cx, pieces), 128, 0, stream, p);
   VB_LAUNCH_PDL(mingru_tile_scan_kernel, dim3(cx, B), 128, 0, stream, p);
-  if (out_dtype == 1) VB_LAUNCH_PDL(mingru_tile_out_kernel<float>, dim3(cx, n_tiles), 128, 0, stream, p);
-  else VB_LAUNCH_PDL(mingru_tile_out_kernel<bf16>, dim3(cx, n_tiles), 128, 0, stream, p);
+  if (out_dtype == 1) VB_LAUNCH_PDL(mingru_tile_out_kernel<float>, dim3(cx, pieces), 128, 0, stream, p);
+  else VB_LAUNCH_PDL(mingru_tile_out_kernel<bf16>, dim3(cx, pieces), 128, 0, stream, p);
   return 0;
+}
+
+int vb_mingru_scratch_floats(int n_tiles, int tile_rows, int width) {
+  return n_tiles * (tile_rows / MG_ROWS) * 2 * width;
 }
 
 }  // extern "C"

@@ -53,37 +53,6 @@ __global__ void embed_rows_kernel(float* __restrict__ out, const WT* __restrict_
   }
 }
 
-// The tail of a pre-norm sublayer with a gated residual, in place on the fp32 row:
-//   x[t] += sigmoid(r[t] + b) * y[t]      (r: the gate's projection of the sublayer's input, b its bias; r == nullptr: x += y)
-//   x[t] += add[t]                        (optional: e.g. the embedding entering a repeated pass over the layers)
-//   out[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w      (optional: what the next sublayer reads)
-template <typename OT>
-__global__ void __launch_bounds__(256) gated_residual_norm_kernel(float* __restrict__ x, const float* __restrict__ y,
-                                                                  const float* __restrict__ r, int ld_r,
-                                                                  const float* __restrict__ bias, const float* __restrict__ add,
-                                                                  OT* __restrict__ out, const float* __restrict__ w, int W,
-                                                                  float eps) {
-  extern __shared__ float sm[];
-  float* row = sm;
-  float* red = sm + W;
-  int phase = 0;
-  pdl_sync();
-  const size_t t = blockIdx.x;
-  float q = 0.f;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    float g = 1.f;
-    if (r) g = 1.f / (1.f + expf(-(r[t * ld_r + i] + (bias ? bias[i] : 0.f))));
-    float v = x[t * W + i] + g * y[t * W + i];
-    if (add) v += add[t * W + i];
-    x[t * W + i] = v;
-    row[i] = v;
-    q = fmaf(v, v, q);
-  }
-  if (out == nullptr) return;
-  const float rs = 1.f / sqrtf(block_sum(q, red, phase) / W + eps);
-  for (int i = threadIdx.x; i < W; i += blockDim.x) out[t * W + i] = from_f<OT>(row[i] * rs * w[i]);
-}
-
 // RMS norm of a row with one or two weights: out1[t] = x[r] / sqrt(mean(x[r]^2) + eps) * w1, out2[t] likewise with w2
 // (the two sublayers of a parallel block read differently weighted norms of the same row)
 template <typename OT>
@@ -160,6 +129,68 @@ template <> __device__ __forceinline__ void store4<float>(float* __restrict__ p,
 }
 template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* __restrict__ p, float a, float b, float c, float d) {
   *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(a, b), pack_bf16(c, d));
+}
+
+// The tail of a pre-norm sublayer with a gated residual, in place on the fp32 row:
+//   x[t] += sigmoid(r[t] + b) * y[t]      (r: the gate's projection of the sublayer's input, b its bias; r == nullptr: x += y)
+//   x[t] += add[t]                        (optional: e.g. the embedding entering a repeated pass over the layers)
+//   out[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w      (optional: what the next sublayer reads)
+template <typename OT>
+__global__ void __launch_bounds__(256) gated_residual_norm_kernel(float* __restrict__ x, const float* __restrict__ y,
+                                                                  const float* __restrict__ r, int ld_r,
+                                                                  const float* __restrict__ bias, const float* __restrict__ add,
+                                                                  OT* __restrict__ out, const float* __restrict__ w, int W,
+                                                                  float eps, int vec) {
+  extern __shared__ float sm[];
+  float* row = sm;
+  float* red = sm + W;
+  int phase = 0;
+  pdl_sync();
+  const size_t t = blockIdx.x;
+  float q = 0.f;
+  if (vec) {
+    // rows that move in 16-byte pieces (width, gate stride and every base pointer allow it): all loads of a piece in flight
+    for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+      const float4 xv = *reinterpret_cast<const float4*>(x + t * W + i);
+      const float4 yv = *reinterpret_cast<const float4*>(y + t * W + i);
+      float4 g = make_float4(1.f, 1.f, 1.f, 1.f);
+      if (r) {
+        const float4 rv = *reinterpret_cast<const float4*>(r + t * ld_r + i);
+        const float4 bv = bias ? *reinterpret_cast<const float4*>(bias + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        g.x = 1.f / (1.f + expf(-(rv.x + bv.x))); g.y = 1.f / (1.f + expf(-(rv.y + bv.y)));
+        g.z = 1.f / (1.f + expf(-(rv.z + bv.z))); g.w = 1.f / (1.f + expf(-(rv.w + bv.w)));
+      }
+      float4 v = make_float4(xv.x + g.x * yv.x, xv.y + g.y * yv.y, xv.z + g.z * yv.z, xv.w + g.w * yv.w);
+      if (add) {
+        const float4 av = *reinterpret_cast<const float4*>(add + t * W + i);
+        v.x += av.x; v.y += av.y; v.z += av.z; v.w += av.w;
+      }
+      *reinterpret_cast<float4*>(x + t * W + i) = v;
+      *reinterpret_cast<float4*>(row + i) = v;
+      q = fmaf(v.x, v.x, q); q = fmaf(v.y, v.y, q); q = fmaf(v.z, v.z, q); q = fmaf(v.w, v.w, q);
+    }
+  } else {
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      float g = 1.f;
+      if (r) g = 1.f / (1.f + expf(-(r[t * ld_r + i] + (bias ? bias[i] : 0.f))));
+      float v = x[t * W + i] + g * y[t * W + i];
+      if (add) v += add[t * W + i];
+      x[t * W + i] = v;
+      row[i] = v;
+      q = fmaf(v, v, q);
+    }
+  }
+  if (out == nullptr) return;
+  const float rs = 1.f / sqrtf(block_sum(q, red, phase) / W + eps);
+  if (vec) {
+    for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(row + i);
+      const float4 wv = *reinterpret_cast<const float4*>(w + i);
+      store4<OT>(out + t * W + i, v.x * rs * wv.x, v.y * rs * wv.y, v.z * rs * wv.z, v.w * rs * wv.w);
+    }
+  } else {
+    for (int i = threadIdx.x; i < W; i += blockDim.x) out[t * W + i] = from_f<OT>(row[i] * rs * w[i]);
+  }
 }
 
 // ROWS rows per CTA: the side matrices are read once per CTA and serve all of its rows (long steps).  A row's result
@@ -683,12 +714,15 @@ int vb_gated_residual_norm_f32(float* d_x, const float* d_y, const float* d_r, i
   if (T <= 0) return 0;
   const size_t smem = (static_cast<size_t>(width) + 64) * sizeof(float);
   VB_CHECK_ARG(smem <= static_cast<size_t>(VB_MAX_DYN_SMEM), "vb_gated_residual_norm_f32: width %d too large", width);
+  auto al16 = [](const void* q) { return q == nullptr || reinterpret_cast<uintptr_t>(q) % 16 == 0; };
+  const int vec = width % 4 == 0 && (!d_r || ld_r % 4 == 0) && al16(d_x) && al16(d_y) && al16(d_r) && al16(d_bias) && al16(d_add) &&
+                  al16(d_w) && (!d_out || reinterpret_cast<uintptr_t>(d_out) % 8 == 0);
   if (out_dtype == 1) {
     if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(gated_residual_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
-    VB_LAUNCH_PDL(gated_residual_norm_kernel<float>, T, 256, smem, stream, d_x, d_y, d_r, ld_r, d_bias, d_add, static_cast<float*>(d_out), d_w, width, eps);
+    VB_LAUNCH_PDL(gated_residual_norm_kernel<float>, T, 256, smem, stream, d_x, d_y, d_r, ld_r, d_bias, d_add, static_cast<float*>(d_out), d_w, width, eps, vec);
   } else {
     if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(gated_residual_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
-    VB_LAUNCH_PDL(gated_residual_norm_kernel<bf16>, T, 256, smem, stream, d_x, d_y, d_r, ld_r, d_bias, d_add, static_cast<bf16*>(d_out), d_w, width, eps);
+    VB_LAUNCH_PDL(gated_residual_norm_kernel<bf16>, T, 256, smem, stream, d_x, d_y, d_r, ld_r, d_bias, d_add, static_cast<bf16*>(d_out), d_w, width, eps, vec);
   }
   return 0;
 }

@@ -168,7 +168,23 @@ struct QkvNormTailParams {
   const int32_t* page_indptr;
   const int32_t* page_indices;
   int page_size, Hq, Gk, Gv, dim, vdim;
+  int stage_lo, stage_hi; // columns of the row staged in shared memory (stage_hi == 0: read from global memory)
 };
+
+// Copies floats [lo, hi) of a projection row into shared memory with every load in flight at once (16-byte loads when the
+// row slice is aligned) and returns a pointer that is indexed like the row itself.  The tails below read a row's values
+// more than once (norm, rotation partner) and from many threads: one pass over DRAM, the rest from shared memory.
+__device__ __forceinline__ const float* stage_row(const float* __restrict__ row, int lo, int hi, float* __restrict__ sm) {
+  const int n = hi - lo;
+  if (((reinterpret_cast<uintptr_t>(row + lo) & 15) == 0) && (n & 3) == 0) {
+    for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4)
+      *reinterpret_cast<float4*>(sm + i) = *reinterpret_cast<const float4*>(row + lo + i);
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) sm[i] = row[lo + i];
+  }
+  __syncthreads();
+  return sm - lo;
+}
 
 __device__ __forceinline__ float rotated_value(const float* __restrict__ src, const float* __restrict__ w, float r,
                                                const float* __restrict__ cs, int half, int layout, int d) {
@@ -186,9 +202,11 @@ __device__ __forceinline__ float rotated_value(const float* __restrict__ src, co
 
 template <typename CT>
 __global__ void __launch_bounds__(256) qkv_norm_rotary_append_kernel(QkvNormTailParams p) {
+  extern __shared__ __align__(16) float tail_sm[];
   pdl_sync();
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float* row = p.proj + static_cast<size_t>(t) * p.ldp;
+  if (p.stage_hi > 0) row = stage_row(row, p.stage_lo, p.stage_hi, tail_sm);
   const int b = p.row_req[t], ps = p.pos[t];
   const size_t tok = static_cast<size_t>(p.page_indices[p.page_indptr[b] + ps / p.page_size]) * p.page_size + ps % p.page_size;
   const float* cs = p.cs ? p.cs + static_cast<size_t>(t) * 2 * p.half : nullptr;
@@ -232,35 +250,42 @@ struct LatentRopeTailParams {
   const int32_t* page_indices;
   int page_size;
   float eps;
+  int stage_lo, stage_hi; // columns of the row staged in shared memory (stage_hi == 0: read from global memory)
 };
 
+constexpr int LR_THREADS = 256;
+
 template <typename CT>
-__global__ void __launch_bounds__(128) latent_rope_append_kernel(LatentRopeTailParams p) {
-  __shared__ float red[4];
+__global__ void __launch_bounds__(LR_THREADS) latent_rope_append_kernel(LatentRopeTailParams p) {
+  extern __shared__ __align__(16) float tail_sm[];
+  __shared__ float red[LR_THREADS / 32];
   pdl_sync();
   const size_t t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float* row = p.proj + t * p.ldp;
+  if (p.stage_hi > 0) row = stage_row(row, p.stage_lo, p.stage_hi, tail_sm);
   const float* c = row + p.c_off;
   const float* cs = p.cs ? p.cs + t * 2 * p.half : nullptr;
   float sc = 0.f;
-  for (int i = threadIdx.x; i < p.kv_rank; i += 128) sc = fmaf(c[i], c[i], sc);
+  for (int i = threadIdx.x; i < p.kv_rank; i += LR_THREADS) sc = fmaf(c[i], c[i], sc);
   sc = warp_sum(sc);
   if (lane == 0) red[warp] = sc;
   __syncthreads();
-  sc = red[0] + red[1] + red[2] + red[3];
+  sc = 0.f;
+#pragma unroll
+  for (int i = 0; i < LR_THREADS / 32; ++i) sc += red[i];
   const float rc = 1.f / sqrtf(sc / p.kv_rank + p.eps);
   const int b = p.row_req[t], ps = p.pos[t];
   const size_t tok = static_cast<size_t>(p.page_indices[p.page_indptr[b] + ps / p.page_size]) * p.page_size + ps % p.page_size;
   const int ldc = p.kv_rank + p.rot;
   CT* co = static_cast<CT*>(p.cache) + tok * ldc;
-  for (int i = threadIdx.x; i < p.kv_rank; i += 128) co[i] = wa_from_f<CT>(c[i] * rc * p.wc[i]);
-  for (int i = threadIdx.x; i < p.rot; i += 128)
+  for (int i = threadIdx.x; i < p.kv_rank; i += LR_THREADS) co[i] = wa_from_f<CT>(c[i] * rc * p.wc[i]);
+  for (int i = threadIdx.x; i < p.rot; i += LR_THREADS)
     co[p.kv_rank + i] = wa_from_f<CT>(rotated_value(c + p.kv_rank, nullptr, 1.f, cs, p.half, p.layout, i));
   const int dq = p.dim + p.rot;
   CT* qo = static_cast<CT*>(p.q_out) + t * p.H * p.dim;
   CT* ql = static_cast<CT*>(p.q_lat) + t * p.H * ldc;
-  for (int i = threadIdx.x; i < p.H * dq; i += 128) {
+  for (int i = threadIdx.x; i < p.H * dq; i += LR_THREADS) {
     const int h = i / dq, d = i - h * dq;
     const float* src = row + p.q_off + h * dq;
     if (d < p.dim) qo[h * p.dim + d] = wa_from_f<CT>(src[d]);
@@ -974,9 +999,21 @@ int vb_qkv_norm_rotary_append(const float* d_proj, int ldp, int q_off, int k_off
   if (T <= 0) return 0;
   QkvNormTailParams p{d_proj, ldp, q_off, k_off, v_off, half > 0 ? d_cs : nullptr, half, layout, d_q_norm, d_k_norm, eps,
                       d_q_out, d_k_cache, d_v_cache, d_row_req, d_pos, d_page_indptr, d_page_indices, page_size, Hq, Gk, Gv,
-                      dim, vdim};
-  if (dtype == 1) VB_LAUNCH_PDL(qkv_norm_rotary_append_kernel<float>, T, 256, 0, stream, p);
-  else VB_LAUNCH_PDL(qkv_norm_rotary_append_kernel<bf16>, T, 256, 0, stream, p);
+                      dim, vdim, 0, 0};
+  // the q | k | v columns of a row are staged in shared memory when they lie side by side and fit
+  const int lo = min(q_off, min(k_off, v_off)), hi = max(q_off + Hq * dim, max(k_off + Gk * dim, v_off + Gv * vdim));
+  size_t smem = 0;
+  if (hi - lo == (Hq + Gk) * dim + Gv * vdim && static_cast<size_t>(hi - lo) * sizeof(float) <= static_cast<size_t>(VB_MAX_DYN_SMEM)) {
+    p.stage_lo = lo; p.stage_hi = hi;
+    smem = static_cast<size_t>(hi - lo) * sizeof(float);
+  }
+  if (dtype == 1) {
+    if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(qkv_norm_rotary_append_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+    VB_LAUNCH_PDL(qkv_norm_rotary_append_kernel<float>, T, 256, smem, stream, p);
+  } else {
+    if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(qkv_norm_rotary_append_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+    VB_LAUNCH_PDL(qkv_norm_rotary_append_kernel<bf16>, T, 256, smem, stream, p);
+  }
   return 0;
 }
 
@@ -992,9 +1029,20 @@ int vb_latent_rope_append(const float* d_proj, int ldp, int q_off, int c_off, in
                H, dim, rot, kv_rank, 2 * half);
   if (T <= 0) return 0;
   LatentRopeTailParams p{d_proj, ldp, q_off, c_off, H, dim, rot, kv_rank, d_wc, half > 0 ? d_cs : nullptr, half, layout,
-                         d_q_out, d_q_lat, d_cache, d_row_req, d_pos, d_page_indptr, d_page_indices, page_size, eps};
-  if (dtype == 1) VB_LAUNCH_PDL(latent_rope_append_kernel<float>, T, 128, 0, stream, p);
-  else VB_LAUNCH_PDL(latent_rope_append_kernel<bf16>, T, 128, 0, stream, p);
+                         d_q_out, d_q_lat, d_cache, d_row_req, d_pos, d_page_indptr, d_page_indices, page_size, eps, 0, 0};
+  const int lo = min(q_off, c_off), hi = max(q_off + H * (dim + rot), c_off + kv_rank + rot);
+  size_t smem = 0;
+  if (hi - lo == H * (dim + rot) + kv_rank + rot && static_cast<size_t>(hi - lo) * sizeof(float) <= static_cast<size_t>(VB_MAX_DYN_SMEM)) {
+    p.stage_lo = lo; p.stage_hi = hi;
+    smem = static_cast<size_t>(hi - lo) * sizeof(float);
+  }
+  if (dtype == 1) {
+    if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(latent_rope_append_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+    VB_LAUNCH_PDL(latent_rope_append_kernel<float>, T, LR_THREADS, smem, stream, p);
+  } else {
+    if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(latent_rope_append_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+    VB_LAUNCH_PDL(latent_rope_append_kernel<bf16>, T, LR_THREADS, smem, stream, p);
+  }
   return 0;
 }
 

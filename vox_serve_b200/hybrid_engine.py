@@ -685,7 +685,8 @@ class HybridEngine:
             self.lin_scratch = torch.zeros(n_t * max(m.heads * m.dim * m.vdim for m in tiled), dtype=F32, device=dev)
         if gru:
             n_t = max_rows // self.lin_tile_rows + max_out_rows + 1
-            self.gru_scratch = torch.zeros(n_t * 2 * max(m.width for m in gru), dtype=F32, device=dev)
+            self.gru_scratch = torch.zeros(ops.mingru_scratch_floats(n_t, self.lin_tile_rows, max(m.width for m in gru))
+                                           if dev.type == "cuda" else 1, dtype=F32, device=dev)
         self.v_first = torch.zeros(R * max([m.kv_heads * m.vdim for m in att if m.v_mix] + [1]), dtype=F32, device=dev)
         # split-key scratch of the per-row attention kernel: steps of up to 256 rows, 8 splits
         self.attn_part = torch.zeros(256 * 8 * max([m.heads * (m.vdim + 2) for m in att] +
@@ -1118,7 +1119,7 @@ class HybridEngine:
         out = self.mix_out[:T * Wm].view(T, Wm)
         state = self.cache.state[ci]
         par = (s.multi and s.tiles is not None and self.use_tiled_recurrence
-               and s.tiles[2] * 2 * Wm <= self.gru_scratch.numel())
+               and ops.mingru_scratch_floats(s.tiles[2], self.lin_tile_rows, Wm) <= self.gru_scratch.numel())
         if s.single or (s.multi and not par):
             ops.mingru(proj, 0, Wm, 2 * Wm, w["z_b"], w["x_b"], state, out, s.qo_indptr, s.pos, s.slots, s.B,
                        single_rows=s.single, multi_rows=s.multi and not par)

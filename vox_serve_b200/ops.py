@@ -1182,6 +1182,10 @@ def mingru(proj: torch.Tensor, z_off: int, x_off: int, g_off: int, bz: Optional[
     return out
 
 
+def mingru_scratch_floats(n_tiles: int, tile_rows: int, width: int) -> int:
+    return _lib.load().vb_mingru_scratch_floats(int(n_tiles), int(tile_rows), int(width))
+
+
 def mingru_tiled(proj: torch.Tensor, z_off: int, x_off: int, g_off: int, bz: Optional[torch.Tensor],
                  bx: Optional[torch.Tensor], state: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor,
                  qo_indptr: torch.Tensor, pos: torch.Tensor, slots: torch.Tensor, tile_req: torch.Tensor,
@@ -1189,7 +1193,8 @@ def mingru_tiled(proj: torch.Tensor, z_off: int, x_off: int, g_off: int, bz: Opt
     """Prompt portions with their tiles processed in parallel (requests that bring one row are not touched)."""
     _need_cuda(proj, state, out, scratch)
     width = state.shape[1]
-    assert proj.dtype == F32 and state.dtype == F32 and scratch.dtype == F32 and scratch.numel() >= n_tiles * 2 * width
+    assert proj.dtype == F32 and state.dtype == F32 and scratch.dtype == F32
+    assert scratch.numel() >= mingru_scratch_floats(n_tiles, tile_rows, width)
     call("vb_mingru_tiled", out.data_ptr(), state.data_ptr(), scratch.data_ptr(), proj.data_ptr(), proj.stride(0), z_off, x_off,
          g_off, _p(bz), _p(bx), qo_indptr.data_ptr(), pos.data_ptr(), slots.data_ptr(), tile_req.data_ptr(),
          tile_row0.data_ptr(), n_tiles, tile_rows, B, width, _dt(out), _stream())
