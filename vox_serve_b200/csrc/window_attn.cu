@@ -11,8 +11,15 @@
 //                        beyond its registers, one warp per (token row, query head).  Online softmax, gate, store.
 //   vb_window_attn_tiled prompt portions: one CTA per (64 query rows of one request, query head), K/V tiles staged in
 //                        shared memory and reused by all rows of the tile: mma.sync tensor-core tiles for bf16 heads whose
-//                        sizes are multiples of 16 up to 128, fp32 FMAs otherwise (and always in fp32 mode).
-// Cache layout per layer: K [pages][page_size][kv_heads][dim], V [pages][page_size][kv_heads][vdim].
+//                        sizes are multiples of 16 (keys up to 192 dims, values up to 128), fp32 FMAs otherwise (and always
+//                        in fp32 mode).
+//   vb_qkv_norm_rotary_append, vb_latent_rope_append, vb_head_pair_combine: projection tails with per-head RMS norms, rotation
+//                        in (2i, 2i + 1) or (i, i + half) pairs, a shared rotated key part behind a latent, and the
+//                        combination of two score maps per head.
+// Besides the sliding window the kernels take a chunk mask (a position sees the keys of its own block of positions), per-token
+// strides of the two caches (a value that is a leading slice of the key row), key heads that share a value head, and an fp32
+// output beside bf16 operands.
+// Cache layout per layer: K [pages][page_size][kv_heads][dim], V [pages][page_size][kv_heads][vdim] unless strides say otherwise.
 #include "../../include/vb_api.h"
 #define VB_PDL_FAMILY 1
 #include "common.cuh"

@@ -17,6 +17,10 @@ of one).  Per layer:
     router -> group by expert -> grouped gate/up (silu * up) -> grouped down -> shared expert -> weighted sum
 each followed (sequential form) by ``x += LayerNorm(y)`` fused with the LayerNorm that feeds the next sublayer, or
 (parallel form) by ``x += m * (mixer + feed-forward)`` fused with the side input and the next block's two RMS norms.
+A third block form, ``gated`` (pre-norm, ``x += sigmoid(W_r h + b) * sublayer(h)``, scalar RMS norms, optionally a span of
+layers run several times with a cache or state per pass), carries three more mixers -- latent attention with direct queries
+and a shared rotated key part, attention with two score maps per head restricted to chunks, minGRU -- and a clamped gated
+feed-forward (``_forward_gated`` at the end of this file).
 
 Precision: ``dtype`` bfloat16 keeps projections' operands, q / k / v, the page cache and the attention output in bf16 with
 fp32 accumulation; norms, softmax, router, residual, recurrent state, decays and the lightning path after its projection
