@@ -653,3 +653,66 @@ def test_greedy_generation_through_scheduler(dtype):
                 wrong += t != int(top.indices[0])
             toks.append(t)
     assert wrong == 0, wrong
+
+
+def _write_model_dir(d, cfg, sd):
+    """config.json + model.safetensors (8-byte length, JSON header, raw little-endian data) of a bfloat16 checkpoint"""
+    import struct
+
+    meta, blobs, off = {}, [], 0
+    for k, v in sd.items():
+        raw = v.contiguous().reshape(-1).view(torch.uint8).numpy().tobytes()
+        meta[k] = {"dtype": "BF16", "shape": list(v.shape), "data_offsets": [off, off + len(raw)]}
+        blobs.append(raw)
+        off += len(raw)
+    head = json.dumps(meta).encode()
+    with open(os.path.join(d, "model.safetensors"), "wb") as f:
+        f.write(struct.pack("<Q", len(head)) + head + b"".join(blobs))
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(cfg, f)
+
+
+@pytest.mark.gpu
+def test_command_lines_on_a_model_directory(capsys):
+    """a checkpoint directory (scalar norm weights as 0-dim tensors) through the trace replay tool (a subprocess: portions,
+    two requests, a request ended and its slot taken again) and through the generate command (in process)."""
+    import subprocess
+    import sys
+
+    import numpy as np
+
+    from vox_serve_b200 import generate
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = O.make_config(layers=("latent", "gru-", "attention", "latent-"), loop=(1, 3, 2))
+    sd = O.random_weights(cfg, 17, head_gain=6.0)
+    V = cfg["vocab"]
+    a, b, c = _tokens(30, V, 1), _tokens(12, V, 2), _tokens(9, V, 3)
+    with tempfile.TemporaryDirectory() as d:
+        _write_model_dir(d, cfg, sd)
+        out = os.path.join(d, "out")
+        steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:20], "want": [0, 19]}, {"id": "b", "tokens": b[:2], "want": []}], "end": []},
+                 {"step": 1, "entries": [{"id": "a", "tokens": a[20:21], "want": [0]}, {"id": "b", "tokens": b[2:], "want": [9]}], "end": ["b"]},
+                 {"step": 2, "entries": [{"id": "c", "tokens": c, "want": [8]}, {"id": "a", "tokens": a[21:], "want": [8]}], "end": ["a", "c"]}]
+        r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", d, "--dtype", "float32", "--out", out,
+                            "--max-tokens", "128"], input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True,
+                           text=True, timeout=900)
+        assert r.returncode == 0, r.stderr[-2000:]
+        assert [ln for ln in r.stdout.splitlines() if ln.startswith("done")] == ["done 0", "done 1", "done 2"]
+        ra, rb, rc = (O.forward(cfg, sd, t)[0] for t in (a, b, c))
+        want = {0: torch.stack([ra[0], ra[19]]), 1: torch.stack([ra[20], rb[11]]), 2: torch.stack([rc[8], ra[29]])}
+        for s_, ref in want.items():
+            got = torch.from_numpy(np.fromfile(os.path.join(out, f"{s_}.f32"), dtype="<f4").reshape(2, V).copy())
+            assert _err(got, ref) < TOL[F32], s_
+        capsys.readouterr()
+        assert generate.main(["--model", d, "--prompt", " ".join(map(str, a)), "--prompt", " ".join(map(str, b)), "--max-new", "6",
+                              "--dtype", "float32", "--prefill-chunk", "16", "--page-size", "8"]) == 0
+        lines = capsys.readouterr().out.strip().splitlines()[-2:]
+        for line, prompt in zip(lines, (a, b)):
+            toks = list(prompt)
+            for t in (int(x) for x in line.split()):
+                z = O.forward(cfg, sd, toks)[0][-1]
+                top = torch.topk(z, 2)
+                assert float(top.values[0] - top.values[1]) < 0.05 or t == int(top.indices[0])
+                toks.append(t)
+            assert len(toks) == len(prompt) + 6
