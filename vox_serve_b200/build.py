@@ -24,8 +24,9 @@ SOURCES = ["api.cu", "elementwise.cu", "attn.cu", "prefill_attn.cu", "prefill_at
            "multicodebook.cu", "mimi.cu", "codec.cu", "norm_linear.cu", "window_attn.cu", "linear_attn.cu", "gated_recurrence.cu", "moe.cu"]
 # subsets of the sources that serve one family of models: a first run that only needs that family compiles only these
 # (into lib/libvoxb200_<profile>.so; entry points of the other sources are absent from it)
-PROFILES = {"text": ["api.cu", "elementwise.cu", "gemm.cu", "sampler.cu", "norm_linear.cu", "window_attn.cu", "linear_attn.cu",
-                     "gated_recurrence.cu", "moe.cu"]}
+_TEXT = ["api.cu", "elementwise.cu", "gemm.cu", "sampler.cu", "norm_linear.cu", "window_attn.cu"]
+PROFILES = {"text": _TEXT + ["linear_attn.cu", "moe.cu"],           # attention + decay attention + mixtures of experts
+            "text_gated": _TEXT + ["gated_recurrence.cu"]}           # attention + element-wise gated recurrence, dense feed-forward
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC",

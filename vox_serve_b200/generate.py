@@ -31,8 +31,9 @@ def main(argv=None) -> int:
     import torch
 
     from . import _lib
+    from .model import build_profile
 
-    _lib.load(build_if_missing=True, profile="text")
+    _lib.load(build_if_missing=True, profile=build_profile(a.model))
     from .requests import Request
     from .sampling import SamplingConfig
     from .scheduler import Scheduler

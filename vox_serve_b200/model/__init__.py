@@ -52,6 +52,12 @@ def get_model_class(model_name: str) -> Type[BaseLM]:
     raise ValueError(f"No model class found for '{model_name}'. Available model patterns: {list(MODEL_REGISTRY)}")
 
 
+def build_profile(model_name: str):
+    """The subset of the CUDA sources (build.PROFILES) that serves the model, or None for the whole library: what a first
+    run without a built library compiles."""
+    return getattr(get_model_class(model_name), "build_profile", None)
+
+
 _OVERRIDES = ("top_p", "top_k", "min_p", "temperature", "max_tokens", "repetition_penalty", "repetition_window",
               "cfg_scale")
 

@@ -97,6 +97,7 @@ class BobavikModel(BaseLM):
     has_recurrent_state = True
     design = "Bobavik"
     synthetic_name = "bobavik-synthetic"
+    build_profile = "text"          # the subset of the CUDA sources (build.PROFILES) a first run of this design compiles
 
     # what a design built on the hybrid engine supplies: its configuration reader and its seeded random weights
     @staticmethod

@@ -132,6 +132,7 @@ class FovunexModel(BobavikModel):
     design = "Fovunex"
     synthetic_name = "fovunex-synthetic"
     has_recurrent_state = True
+    build_profile = "text_gated"
 
     @staticmethod
     def read_config(config: Dict[str, Any]) -> HybridConfig:
