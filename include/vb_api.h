@@ -480,7 +480,8 @@ int vb_gemm_bf16_grouped(void* d_y, const void* d_w_tiles, const void* x_map, in
                          int tile_rows, int n_out, int t_tile, const int32_t* d_tile_group, long long group_bytes,
                          int w_kb_stride, int group_kb, int kb_base, int act, void* stream);
 
-/* ---- hybrid decoder stacks with an fp32 residual stream (norm_linear.cu, window_attn.cu, linear_attn.cu, moe.cu) ----
+/* ---- hybrid decoder stacks with an fp32 residual stream (norm_linear.cu, window_attn.cu, linear_attn.cu,
+ * gated_recurrence.cu, moe.cu) ----
  * dtype arguments: 0 = bf16, 1 = fp32.  Norm weights, router weights, decays and recurrent states are always fp32.
  * vb_embed_rows_f32:        out[t] = table[ids[t]] widened to fp32 (+ pos_table[pos[t]] when a table of learned positions
  *                           [n_pos][width] of the same type is given)

@@ -119,9 +119,10 @@ class DecayAttentionConfig:
 
 @dataclass
 class LatentAttentionConfig:
-    """Causal softmax attention without positional rotation whose queries go through a normed latent of q_rank dims and
-    whose keys and values are per-head expansions of ONE normed latent of kv_rank dims per token -- the only thing cached.
-    kv_from: the layer whose cached latents this layer reads instead of projecting its own.  One sigmoid gate per head."""
+    """Causal softmax attention whose keys and values are per-head expansions of ONE normed latent of kv_rank dims per token
+    -- with the shared rotated key part, if there is one, the only thing cached.  Queries go through a normed latent of
+    q_rank dims, or come straight from the input (q_rank = 0).  kv_from: the layer whose cached latents this layer reads
+    instead of projecting its own.  head_gate: one sigmoid gate per head."""
     heads: int
     dim: int
     vdim: int

@@ -921,7 +921,8 @@ def orpheus_window_codes(ids: torch.Tensor, audio_id_base: int):
 
 
 # ----------------------------------------------------------------------------------------------
-# hybrid decoder stacks with an fp32 residual stream (norm_linear.cu, window_attn.cu, linear_attn.cu, moe.cu)
+# hybrid decoder stacks with an fp32 residual stream (norm_linear.cu, window_attn.cu, linear_attn.cu, gated_recurrence.cu,
+# moe.cu)
 # dtype codes of the C ABI: 0 = bf16, 1 = fp32
 # ----------------------------------------------------------------------------------------------
 F32 = torch.float32
