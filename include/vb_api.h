@@ -479,6 +479,10 @@ int vb_gemm_bf16_glu(void* d_y, const void* d_w_tiles, const void* x_map, int T,
 int vb_gemm_bf16_grouped(void* d_y, const void* d_w_tiles, const void* x_map, int T, int N, int K, int ldy, int mode,
                          int tile_rows, int n_out, int t_tile, const int32_t* d_tile_group, long long group_bytes,
                          int w_kb_stride, int group_kb, int kb_base, int act, void* stream);
+/* the grouped form of vb_gemm_bf16_glu (matrices stacked along N) */
+int vb_gemm_bf16_grouped_glu(void* d_y, const void* d_w_tiles, const void* x_map, int T, int N, int K, int ldy, int tile_rows,
+                             int n_out, int t_tile, const int32_t* d_tile_group, long long group_bytes, float limit,
+                             float slope, void* stream);
 
 /* ---- hybrid decoder stacks with an fp32 residual stream (norm_linear.cu, window_attn.cu, linear_attn.cu,
  * gated_recurrence.cu, moe.cu) ----
@@ -641,6 +645,11 @@ int vb_moe_route(int32_t* d_idx, float* d_wts, const void* d_h, const float* d_r
 int vb_moe_route_sigmoid(int32_t* d_idx, float* d_wts, float* d_shared_gate, const void* d_h, const float* d_router_w,
                          const float* d_correction, const float* d_shared_gate_w, int T, int width, int experts, int top,
                          int n_groups, int keep, int h_dtype, void* stream);
+/* the general form: softmax_scores != 0: s = softmax(W_r h) over all experts instead of the sigmoid; rank_by_max != 0: a
+ * group's score is its largest corrected score; normalize == 0: weights are the chosen scores themselves */
+int vb_moe_route_groups(int32_t* d_idx, float* d_wts, float* d_shared_gate, const void* d_h, const float* d_router_w,
+                        const float* d_correction, const float* d_shared_gate_w, int T, int width, int experts, int top,
+                        int n_groups, int keep, int softmax_scores, int rank_by_max, int normalize, int h_dtype, void* stream);
 int vb_moe_group(int32_t* d_row_off, int32_t* d_sorted_token, int32_t* d_pair_row, const int32_t* d_idx, int T,
                  int experts, int top, int tile_rows, int32_t* d_tile_group, int n_tiles, void* stream);
 /* (tile_rows > 0: every expert's rows start at a multiple of tile_rows; padding rows get token -1; d_tile_group[i] =
@@ -655,6 +664,74 @@ int vb_moe_scale_dense(void* d_act, const int32_t* d_idx, const float* d_wts, in
 int vb_moe_combine(float* d_y, const float* d_expert_out, const float* d_shared_out, const float* d_wts,
                    const int32_t* d_pair_row, int T, int width, int top, const float* d_shared_scale, void* stream);
 /* (d_shared_scale [T], optional: the shared expert's output enters times that per-token factor) */
+
+/* ---- post-norm stacks with short convolutions, pooled-window sigmoid attention and a selective scan (norm_linear.cu,
+ * short_conv.cu, sigmoid_attn.cu, selective_scan.cu) ----
+ * vb_rms_postnorm_residual_f32: x[t] += y[t] / sqrt(mean(y[t]^2) + eps) * w in place (fp32); d_out (optional): x[t] in the
+ *   compute type.
+ * vb_linear_batched_gated: vb_linear_batched whose gate holds one value per output value (gate_per_value != 0: column
+ *   g * N + n of the gate row) instead of one per group.
+ * vb_pair_hash_rows: rows[t] = (prev * mul_prev + ids[t] * mul_cur) mod buckets, `buckets` for a request's first token; the
+ *   token before a step's first row comes from d_prev_tok[slot], which then takes the step's last token.
+ * vb_short_conv: causal convolution over time per channel of the fp32 columns d_in[t][0 .. channels), weights fp32
+ *   [channels][taps] (last column: the current token), optional bias, act 1 = silu, residual != 0: the input is added to the
+ *   result; d_state [slots][taps - 1][channels] holds a request's last inputs and is advanced by the step (two launches).
+ *   Output in the compute type (d_out) and / or fp32 (d_out_f32).
+ * vb_cast_rows: d_out [T][n] (dense, compute type) = d_in[t][0 .. n) (fp32 rows of stride ld_in).
+ * vb_qk_norm_append: tail of a (q | k | v) projection: q and k RMS-normed over their whole width nq / nk with per-coordinate
+ *   weights (NULL: no norm), q to d_q_out [T][nq], k and v appended to pages [pages][page][nk] / [pages][page][nv].
+ * vb_pool_blocks: for every block of `pool` positions that the step's rows complete, the mean of its cached keys / values into
+ *   the fp32 pooled caches [pages][ceil(page / pool)][nk] / [..][nv] (block b sits in the page of position b * pool, at
+ *   (b * pool mod page) / pool).
+ * vb_sigmoid_attn: out[t][h * vdim ..] = out_scale * sum_j sigmoid(cap(q . k_j * scale) + head_bias[h]) v_j over the window's
+ *   tokens and the pooled blocks wholly before the window (cap(s) = cap * tanh(s / cap) when cap > 0).  Tiles (d_tile_req
+ *   != NULL: rows d_tile_row0[i] .. of request d_tile_req[i], tile_rows each) or single rows (d_row_list, or rows 0 .. n_rows);
+ *   d_part (optional, single rows): scratch for dealing a row's keys to several CTAs, max_keys the most keys a row can see.
+ * vb_selective_scan / _tiled: S[c][n] = exp(dt A[c][n]) S[c][n] + dt x[c] B[n], y[c] = sum_n S[c][n] C[n] + D[c] x[c],
+ *   out = out_scale * y * silu(z), dt = softplus(d_dt + dt_bias); state fp32 [slots][inner][states], zero before position 0.
+ *   The tiled form processes prompt portions in pieces of vb_selective_scan_piece_rows() rows in parallel (scratch:
+ *   vb_selective_scan_scratch_floats floats). */
+int vb_rms_postnorm_residual_f32(float* d_x, const float* d_y, const float* d_w, void* d_out, int T, int width, float eps,
+                                 int out_dtype, void* stream);
+int vb_linear_batched_gated(void* d_out, const void* d_x, const void* d_w, int T, int N, int K, int ldx, int ldo,
+                            long long x_group_stride, long long o_group_stride, long long w_group_stride, int groups,
+                            int in_dtype, int out_dtype, int epilogue, float alpha, const float* d_gate, int ld_gate,
+                            int gate_per_value, void* stream);
+int vb_pair_hash_rows(int32_t* d_rows, int32_t* d_prev_tok, const int32_t* d_ids, const int32_t* d_qo_indptr,
+                      const int32_t* d_row_req, const int32_t* d_pos, const int32_t* d_slots, int T, int buckets,
+                      long long mul_prev, long long mul_cur, void* stream);
+int vb_short_conv(void* d_out, int ld_out, float* d_out_f32, int ld_f32, const float* d_in, int ld_in, const float* d_w,
+                  const float* d_bias, float* d_state, const int32_t* d_qo_indptr, const int32_t* d_row_req, const int32_t* d_pos,
+                  const int32_t* d_slots, int T, int B, int channels, int taps, int act, int residual, int out_dtype,
+                  void* stream);
+int vb_cast_rows(void* d_out, const float* d_in, int ld_in, int T, int n, int out_dtype, void* stream);
+int vb_qk_norm_append(const float* d_proj, int ldp, int q_off, int k_off, int v_off, const float* d_q_norm,
+                      const float* d_k_norm, float eps, void* d_q_out, void* d_k_cache, void* d_v_cache,
+                      const int32_t* d_row_req, const int32_t* d_pos, const int32_t* d_page_indptr,
+                      const int32_t* d_page_indices, int page_size, int T, int nq, int nk, int nv, int dtype, void* stream);
+int vb_pool_blocks(float* d_kp, float* d_vp, const void* d_k_cache, const void* d_v_cache, const int32_t* d_qo_indptr,
+                   const int32_t* d_pos, const int32_t* d_page_indptr, const int32_t* d_page_indices, int page_size, int pool,
+                   int T, int B, int nk, int nv, int dtype, void* stream);
+int vb_sigmoid_attn(void* d_out, int ld_out, const void* d_q, const void* d_k_cache, const void* d_v_cache, const float* d_kp,
+                    const float* d_vp, const float* d_head_bias, const int32_t* d_row_req, const int32_t* d_pos,
+                    const int32_t* d_page_indptr, const int32_t* d_page_indices, const int32_t* d_qo_indptr,
+                    const int32_t* d_tile_req, const int32_t* d_tile_row0, int n_tiles, int tile_rows,
+                    const int32_t* d_row_list, int n_rows, int H, int G, int dim, int vdim, int page_size, int window, int pool,
+                    float scale, float cap, float out_scale, float* d_part, long long part_floats, int max_keys, int dtype,
+                    void* stream);
+int vb_selective_scan_piece_rows(void);
+int vb_selective_scan_scratch_floats(int n_tiles, int tile_rows, int inner, int states);
+int vb_selective_scan(void* d_out, int ld_out, float* d_state, const float* d_x, int ld_x, const float* d_dt, int ld_dt,
+                      const float* d_dt_bias, const float* d_bc, int ld_bc, int b_off, int c_off, const float* d_z, int ld_z,
+                      const float* d_A, const float* d_D, const int32_t* d_qo_indptr, const int32_t* d_pos,
+                      const int32_t* d_slots, int B, int inner, int states, float out_scale, int single_rows, int multi_rows,
+                      int out_dtype, void* stream);
+int vb_selective_scan_tiled(void* d_out, int ld_out, float* d_state, float* d_scratch, const float* d_x, int ld_x,
+                            const float* d_dt, int ld_dt, const float* d_dt_bias, const float* d_bc, int ld_bc, int b_off,
+                            int c_off, const float* d_z, int ld_z, const float* d_A, const float* d_D,
+                            const int32_t* d_qo_indptr, const int32_t* d_pos, const int32_t* d_slots,
+                            const int32_t* d_tile_req, const int32_t* d_tile_row0, int n_tiles, int tile_rows, int B, int inner,
+                            int states, float out_scale, int out_dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -151,6 +151,28 @@ SIGNATURES = {
                                      c_int, c_int, c_int, c_int, P]),
     "vb_moe_combine": (c_int, [P, P, P, P, P, c_int, c_int, c_int, P, P]),
     "vb_moe_scale_dense": (c_int, [P, P, P, c_int, c_int, c_int, c_int, c_int, P, c_int, P]),
+    "vb_gemm_bf16_grouped_glu": (c_int, [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, C.c_longlong, c_float,
+                                         c_float, P]),
+    "vb_moe_route_groups": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                    P]),
+    "vb_rms_postnorm_residual_f32": (c_int, [P, P, P, P, c_int, c_int, c_float, c_int, P]),
+    "vb_linear_batched_gated": (c_int, [P, P, P, c_int, c_int, c_int, c_int, c_int, C.c_longlong, C.c_longlong, C.c_longlong,
+                                        c_int, c_int, c_int, c_int, c_float, P, c_int, c_int, P]),
+    "vb_pair_hash_rows": (c_int, [P, P, P, P, P, P, P, c_int, c_int, C.c_longlong, C.c_longlong, P]),
+    "vb_short_conv": (c_int, [P, c_int, P, c_int, P, c_int, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                              P]),
+    "vb_cast_rows": (c_int, [P, P, c_int, c_int, c_int, c_int, P]),
+    "vb_qk_norm_append": (c_int, [P, c_int, c_int, c_int, c_int, P, P, c_float, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int,
+                                  c_int, c_int, P]),
+    "vb_pool_blocks": (c_int, [P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P]),
+    "vb_sigmoid_attn": (c_int, [P, c_int, P, P, P, P, P, P, P, P, P, P, P, P, P, c_int, c_int, P, c_int, c_int, c_int, c_int,
+                                c_int, c_int, c_int, c_int, c_float, c_float, c_float, P, C.c_longlong, c_int, c_int, P]),
+    "vb_selective_scan_piece_rows": (c_int, []),
+    "vb_selective_scan_scratch_floats": (c_int, [c_int, c_int, c_int, c_int]),
+    "vb_selective_scan": (c_int, [P, c_int, P, P, c_int, P, c_int, P, P, c_int, c_int, c_int, P, c_int, P, P, P, P, P, c_int,
+                                  c_int, c_int, c_float, c_int, c_int, c_int, P]),
+    "vb_selective_scan_tiled": (c_int, [P, c_int, P, P, P, c_int, P, c_int, P, P, c_int, c_int, c_int, P, c_int, P, P, P, P, P,
+                                        P, P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, P]),
 }
 
 _lock = threading.Lock()
@@ -212,7 +234,9 @@ def check(rc: int, what: str = ""):
 # kernels (+ memset nodes) each entry point enqueues; everything not listed launches exactly one
 LAUNCHES = {"vb_set_pdl": 0, "vb_set_trace": 0, "vb_weight_tiles_bytes": 0, "vb_tensor_map_kv": 0,
             "vb_tensor_map_2d_bf16": 0, "vb_device_info": 0, "vb_sample": 1, "vb_update_repetition_cache": 1,
-            "vb_set_gemm_smem_kb": 0, "vb_window_attn_tile_rows": 0, "vb_decay_attn_tile_rows": 0, "vb_decay_attn_tiled": 3, "vb_window_attn": 2, "vb_mingru_tiled": 3, "vb_mingru_scratch_floats": 0}
+            "vb_set_gemm_smem_kb": 0, "vb_window_attn_tile_rows": 0, "vb_decay_attn_tile_rows": 0, "vb_decay_attn_tiled": 3, "vb_window_attn": 2, "vb_mingru_tiled": 3, "vb_mingru_scratch_floats": 0,
+            "vb_short_conv": 2, "vb_selective_scan_tiled": 3, "vb_selective_scan_piece_rows": 0,
+            "vb_selective_scan_scratch_floats": 0, "vb_sigmoid_attn": 1}
 launch_counter = [0]
 
 

@@ -21,12 +21,14 @@ LIB = os.path.join(LIBDIR, "libvoxb200.so")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
 SOURCES = ["api.cu", "elementwise.cu", "attn.cu", "prefill_attn.cu", "prefill_attn_tc.cu", "kvcopy.cu", "encoder.cu", "gemm.cu", "sampler.cu", "snac.cu", "snac_mma.cu",
-           "multicodebook.cu", "mimi.cu", "codec.cu", "norm_linear.cu", "window_attn.cu", "linear_attn.cu", "gated_recurrence.cu", "moe.cu"]
+           "multicodebook.cu", "mimi.cu", "codec.cu", "norm_linear.cu", "window_attn.cu", "linear_attn.cu", "gated_recurrence.cu", "moe.cu", "short_conv.cu", "sigmoid_attn.cu", "selective_scan.cu"]
 # subsets of the sources that serve one family of models: a first run that only needs that family compiles only these
 # (into lib/libvoxb200_<profile>.so; entry points of the other sources are absent from it)
 _TEXT = ["api.cu", "elementwise.cu", "gemm.cu", "sampler.cu", "norm_linear.cu", "window_attn.cu"]
 PROFILES = {"text": _TEXT + ["linear_attn.cu", "moe.cu"],           # attention + decay attention + mixtures of experts
-            "text_gated": _TEXT + ["gated_recurrence.cu"]}           # attention + element-wise gated recurrence, dense feed-forward
+            "text_gated": _TEXT + ["gated_recurrence.cu"],           # attention + element-wise gated recurrence, dense feed-forward
+            # attention + short convolutions + pooled-window sigmoid attention + selective scan + mixtures of experts
+            "text_conv": _TEXT + ["moe.cu", "short_conv.cu", "sigmoid_attn.cu", "selective_scan.cu"]}
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC",

@@ -772,6 +772,25 @@ int vb_gemm_bf16_grouped(void* d_y, const void* d_w_tiles, const void* x_map, in
   return launch_gemm(p, d_w_tiles, x_map, static_cast<cudaStream_t>(stream), nullptr);
 }
 
+// the grouped form of vb_gemm_bf16_glu: row tiles multiplied by their group's interleaved gate / up rows, clamped gated
+// activation on the fp32 sums
+int vb_gemm_bf16_grouped_glu(void* d_y, const void* d_w_tiles, const void* x_map, int T, int N, int K, int ldy, int tile_rows,
+                             int n_out, int t_tile, const int32_t* d_tile_group, long long group_bytes, float limit,
+                             float slope, void* stream) {
+  VB_CHECK_ARG(d_y && d_w_tiles && x_map, "vb_gemm_bf16_grouped_glu: null pointer");
+  VB_CHECK_ARG(tile_rows % 32 == 0 && N % tile_rows == 0 && limit > 0.f,
+               "vb_gemm_bf16_grouped_glu: needs tile_rows %% 32 == 0, N %% tile_rows == 0 and a positive limit");
+  VB_CHECK_ARG(t_tile >= 16 && t_tile <= 256 && t_tile % 16 == 0 && group_bytes >= 0, "vb_gemm_bf16_grouped_glu: t_tile %d", t_tile);
+  GemmParams p = {};
+  p.y = d_y; p.T = T; p.N = N; p.K = K; p.ldy = ldy; p.mode = GM_SILU; p.split_k = 1;
+  p.tile_rows = tile_rows;
+  p.n_out = n_out > 0 ? n_out : N / 2;
+  p.t_tile = t_tile;
+  p.glu_limit = limit; p.glu_slope = slope;
+  p.tile_group = d_tile_group; p.group_bytes = group_bytes;
+  return launch_gemm(p, d_w_tiles, x_map, static_cast<cudaStream_t>(stream), nullptr);
+}
+
 size_t vb_norm_lmhead_workspace_bytes(int T, int K) {
   if (T <= 0 || K <= 0) return 0;
   const int t_tile = vb_gemm_t_tile(T);

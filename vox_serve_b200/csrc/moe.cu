@@ -103,7 +103,8 @@ __global__ void __launch_bounds__(256) moe_route_sigmoid_kernel(int32_t* __restr
                                                                 float* __restrict__ shared_gate, const XT* __restrict__ h,
                                                                 const float* __restrict__ wr, const float* __restrict__ corr,
                                                                 const float* __restrict__ wsg, int W, int E, int top,
-                                                                int n_groups, int keep) {
+                                                                int n_groups, int keep, int softmax_scores, int rank_by_max,
+                                                                int normalize) {
   extern __shared__ float sm[];
   float* sc = sm;               // [E] sigmoid scores
   float* ch = sm + E;           // [E] choice scores (score + correction; -inf once taken or outside the kept groups)
@@ -134,7 +135,7 @@ __global__ void __launch_bounds__(256) moe_route_sigmoid_kernel(int32_t* __restr
     if (lane == 0) {
       const float sg = 1.f / (1.f + expf(-s));
       if (e < E) {
-        sc[e] = sg;
+        sc[e] = softmax_scores ? s : sg;
         ch[e] = sg + (corr ? corr[e] : 0.f);
       } else {
         shared_gate[t] = sg;
@@ -143,6 +144,21 @@ __global__ void __launch_bounds__(256) moe_route_sigmoid_kernel(int32_t* __restr
   }
   __syncthreads();
   if (warp != 0) return;
+  if (softmax_scores) {
+    // scores = softmax of the logits over ALL experts (fp32); they also rank the experts
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, sc[e]);
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) sum += expf(sc[e] - mx);
+    sum = warp_sum(sum);
+    for (int e = lane; e < E; e += 32) {
+      const float v = expf(sc[e] - mx) / sum;
+      sc[e] = v;
+      ch[e] = v + (corr ? corr[e] : 0.f);
+    }
+    __syncwarp();
+  }
   if (n_groups > 1 && keep < n_groups) {
     const int size = E / n_groups;
     for (int g = lane; g < n_groups; g += 32) {
@@ -152,7 +168,7 @@ __global__ void __launch_bounds__(256) moe_route_sigmoid_kernel(int32_t* __restr
         if (v > a) { b = a; a = v; }
         else if (v > b) b = v;
       }
-      gs[g] = size > 1 ? a + b : a;
+      gs[g] = (size > 1 && !rank_by_max) ? a + b : a;
     }
     __syncwarp();
     // `keep` rounds of arg-max mark the kept groups with -inf; the experts of all other groups leave the choice
@@ -182,7 +198,7 @@ __global__ void __launch_bounds__(256) moe_route_sigmoid_kernel(int32_t* __restr
     }
     __syncwarp();
   }
-  if (lane < top) wts[t * top + lane] = my_val / (denom + 1e-20f);
+  if (lane < top) wts[t * top + lane] = normalize ? my_val / (denom + 1e-20f) : my_val;
 }
 
 // single CTA: E <= 1024 experts, any number of pairs
@@ -330,6 +346,13 @@ int vb_moe_route(int32_t* d_idx, float* d_wts, const void* d_h, const float* d_r
 int vb_moe_route_sigmoid(int32_t* d_idx, float* d_wts, float* d_shared_gate, const void* d_h, const float* d_router_w,
                          const float* d_correction, const float* d_shared_gate_w, int T, int width, int experts, int top,
                          int n_groups, int keep, int h_dtype, void* stream) {
+  return vb_moe_route_groups(d_idx, d_wts, d_shared_gate, d_h, d_router_w, d_correction, d_shared_gate_w, T, width, experts, top,
+                             n_groups, keep, 0, 0, 1, h_dtype, stream);
+}
+
+int vb_moe_route_groups(int32_t* d_idx, float* d_wts, float* d_shared_gate, const void* d_h, const float* d_router_w,
+                        const float* d_correction, const float* d_shared_gate_w, int T, int width, int experts, int top,
+                        int n_groups, int keep, int softmax_scores, int rank_by_max, int normalize, int h_dtype, void* stream) {
   VB_CHECK_ARG(d_idx && d_wts && d_h && d_router_w, "vb_moe_route_sigmoid: null pointer");
   VB_CHECK_ARG(experts >= 1 && experts <= 1024 && top >= 1 && top <= 32 && top <= experts,
                "vb_moe_route_sigmoid: experts %d (<= 1024), top %d (<= 32, <= experts)", experts, top);
@@ -341,8 +364,8 @@ int vb_moe_route_sigmoid(int32_t* d_idx, float* d_wts, float* d_shared_gate, con
   const int ng = n_groups > 1 ? n_groups : 1;
   const size_t smem = (2 * static_cast<size_t>(experts) + ng + width) * sizeof(float);
   VB_CHECK_ARG(smem <= 48 * 1024, "vb_moe_route_sigmoid: width %d too large", width);
-  if (h_dtype == 1) VB_LAUNCH_PDL(moe_route_sigmoid_kernel<float>, T, 256, smem, stream, d_idx, d_wts, d_shared_gate, static_cast<const float*>(d_h), d_router_w, d_correction, d_shared_gate_w, width, experts, top, ng, keep);
-  else VB_LAUNCH_PDL(moe_route_sigmoid_kernel<__nv_bfloat16>, T, 256, smem, stream, d_idx, d_wts, d_shared_gate, static_cast<const __nv_bfloat16*>(d_h), d_router_w, d_correction, d_shared_gate_w, width, experts, top, ng, keep);
+  if (h_dtype == 1) VB_LAUNCH_PDL(moe_route_sigmoid_kernel<float>, T, 256, smem, stream, d_idx, d_wts, d_shared_gate, static_cast<const float*>(d_h), d_router_w, d_correction, d_shared_gate_w, width, experts, top, ng, keep, softmax_scores, rank_by_max, normalize);
+  else VB_LAUNCH_PDL(moe_route_sigmoid_kernel<__nv_bfloat16>, T, 256, smem, stream, d_idx, d_wts, d_shared_gate, static_cast<const __nv_bfloat16*>(d_h), d_router_w, d_correction, d_shared_gate_w, width, experts, top, ng, keep, softmax_scores, rank_by_max, normalize);
   return 0;
 }
 

@@ -80,6 +80,32 @@ __global__ void rmsnorm2_kernel(OT* __restrict__ out1, OT* __restrict__ out2, co
   }
 }
 
+// Norm on a sublayer's OUTPUT only, in place on the fp32 stream: x[t] += y[t] / sqrt(mean(y[t]^2) + eps) * w, and (optional)
+// out[t] = x[t] in the compute type: what a following sublayer reads when it takes the stream itself, un-normed.
+template <typename OT>
+__global__ void __launch_bounds__(256) rms_postnorm_residual_kernel(float* __restrict__ x, const float* __restrict__ y,
+                                                                    const float* __restrict__ w, OT* __restrict__ out, int W,
+                                                                    float eps) {
+  extern __shared__ float sm[];
+  float* row = sm;
+  float* red = sm + W;
+  int phase = 0;
+  pdl_sync();
+  const size_t t = blockIdx.x;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = y[t * W + i];
+    row[i] = v;
+    q = fmaf(v, v, q);
+  }
+  const float rs = 1.f / sqrtf(block_sum(q, red, phase) / W + eps);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = x[t * W + i] + row[i] * rs * w[i];
+    x[t * W + i] = v;
+    if (out) out[t * W + i] = from_f<OT>(v);
+  }
+}
+
 __device__ __forceinline__ float act_apply(float v, int act) {
   // 2: relu(v)^2   3: gelu, exact (erf)   4: gelu, tanh form
   if (act == 2) { const float r = fmaxf(v, 0.f); return r * r; }
@@ -502,6 +528,7 @@ struct LinearParams {
   long long x_group_stride, o_group_stride;     // batched form (both 0 otherwise)
   const float* gate;
   int ld_gate;
+  int gate_values;              // batched form: 0 = one gate per (row, group); N = one per output value (column g * N + n)
   // epilogue 1 with glu_limit > 0: the clamped form g' = min(gate, limit), u' = clamp(up, -limit, limit),
   // out = g' * sigmoid(glu_slope * g') * (u' + 1)
   float glu_limit, glu_slope;
@@ -570,11 +597,13 @@ __global__ void __launch_bounds__(256) linear_kernel(LinearParams p) {
     const int r = m0 + ty * 4 + i;
     if (r >= r_hi) continue;
     float gmul = 1.f;
-    if (p.gate) gmul = 1.f / (1.f + expf(-p.gate[static_cast<size_t>(r) * p.ld_gate + blockIdx.z]));
+    if (p.gate && !p.gate_values) gmul = 1.f / (1.f + expf(-p.gate[static_cast<size_t>(r) * p.ld_gate + blockIdx.z]));
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tx * 4 + j;
       if (n >= p.N) continue;
+      if (p.gate && p.gate_values)
+        gmul = 1.f / (1.f + expf(-p.gate[static_cast<size_t>(r) * p.ld_gate + static_cast<size_t>(blockIdx.z) * p.gate_values + n]));
       float v;
       if (EPI == 1) {
         float g = acc[0][i][j], u = acc[NB - 1][i][j];
@@ -644,13 +673,19 @@ __global__ void __launch_bounds__(128) linear_batched_mma_kernel(LinearParams p)
     const int r = m0 + warp * 16 + (lane >> 2) + 8 * half;
     if (r >= p.T) continue;
     float gmul = p.alpha;
-    if (p.gate) gmul *= 1.f / (1.f + expf(-p.gate[static_cast<size_t>(r) * p.ld_gate + z]));
+    if (p.gate && !p.gate_values) gmul *= 1.f / (1.f + expf(-p.gate[static_cast<size_t>(r) * p.ld_gate + z]));
 #pragma unroll
     for (int n = 0; n < BM_N / 8; ++n) {
       const int c = n0 + n * 8 + (lane & 3) * 2;
-      if (c < p.N)
-        *reinterpret_cast<uint32_t*>(out + static_cast<size_t>(r) * p.ldo + c) =
-            pack_bf16(acc[n][2 * half] * gmul, acc[n][2 * half + 1] * gmul);
+      if (c >= p.N) continue;
+      float g0 = gmul, g1 = gmul;
+      if (p.gate && p.gate_values) {
+        const float* gv = p.gate + static_cast<size_t>(r) * p.ld_gate + static_cast<size_t>(z) * p.gate_values + c;
+        g0 *= 1.f / (1.f + expf(-gv[0]));
+        g1 *= 1.f / (1.f + expf(-gv[1]));
+      }
+      *reinterpret_cast<uint32_t*>(out + static_cast<size_t>(r) * p.ldo + c) =
+          pack_bf16(acc[n][2 * half] * g0, acc[n][2 * half + 1] * g1);
     }
   }
 }
@@ -784,6 +819,22 @@ int vb_residual_side_f32(float* d_x, const float* d_y1, const float* d_y2, float
   return out_dtype == 1 ? launch_residual_side<bf16, float>(p, T, s) : launch_residual_side<bf16, bf16>(p, T, s);
 }
 
+int vb_rms_postnorm_residual_f32(float* d_x, const float* d_y, const float* d_w, void* d_out, int T, int width, float eps,
+                                 int out_dtype, void* stream) {
+  VB_CHECK_ARG(d_x && d_y && d_w && width > 0, "vb_rms_postnorm_residual_f32: bad arguments");
+  if (T <= 0) return 0;
+  const size_t smem = (static_cast<size_t>(width) + 64) * sizeof(float);
+  VB_CHECK_ARG(smem <= static_cast<size_t>(VB_MAX_DYN_SMEM), "vb_rms_postnorm_residual_f32: width %d too large", width);
+  if (out_dtype == 1) {
+    if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(rms_postnorm_residual_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+    VB_LAUNCH_PDL(rms_postnorm_residual_kernel<float>, T, 256, smem, stream, d_x, d_y, d_w, static_cast<float*>(d_out), width, eps);
+  } else {
+    if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(rms_postnorm_residual_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+    VB_LAUNCH_PDL(rms_postnorm_residual_kernel<bf16>, T, 256, smem, stream, d_x, d_y, d_w, static_cast<bf16*>(d_out), width, eps);
+  }
+  return 0;
+}
+
 int vb_softcap_f32(float* d_x, long long n, float cap, void* stream) {
   VB_CHECK_ARG(d_x && cap > 0.f, "vb_softcap_f32: bad arguments");
   if (n <= 0) return 0;
@@ -794,12 +845,20 @@ int vb_softcap_f32(float* d_x, long long n, float cap, void* stream) {
 int vb_linear_batched(void* d_out, const void* d_x, const void* d_w, int T, int N, int K, int ldx, int ldo,
                       long long x_group_stride, long long o_group_stride, long long w_group_stride, int groups, int in_dtype,
                       int out_dtype, int epilogue, float alpha, const float* d_gate, int ld_gate, void* stream) {
+  return vb_linear_batched_gated(d_out, d_x, d_w, T, N, K, ldx, ldo, x_group_stride, o_group_stride, w_group_stride, groups,
+                                 in_dtype, out_dtype, epilogue, alpha, d_gate, ld_gate, 0, stream);
+}
+
+int vb_linear_batched_gated(void* d_out, const void* d_x, const void* d_w, int T, int N, int K, int ldx, int ldo,
+                            long long x_group_stride, long long o_group_stride, long long w_group_stride, int groups,
+                            int in_dtype, int out_dtype, int epilogue, float alpha, const float* d_gate, int ld_gate,
+                            int gate_per_value, void* stream) {
   VB_CHECK_ARG(d_out && d_x && d_w && N > 0 && K > 0 && groups >= 1, "vb_linear_batched: bad arguments");
   VB_CHECK_ARG(epilogue == 0 || (epilogue >= 2 && epilogue <= 4), "vb_linear_batched: epilogue %d", epilogue);
-  VB_CHECK_ARG(!d_gate || ld_gate >= groups, "vb_linear_batched: gate rows hold one value per group");
+  VB_CHECK_ARG(!d_gate || ld_gate >= groups * (gate_per_value ? N : 1), "vb_linear_batched: gate rows hold one value per group (or per output value)");
   if (T <= 0) return 0;
   LinearParams p{d_out, d_x, d_w, nullptr, nullptr, T, N, K, ldx, ldo, epilogue, w_group_stride, alpha, x_group_stride,
-                 o_group_stride, d_gate, ld_gate};
+                 o_group_stride, d_gate, ld_gate, (d_gate && gate_per_value) ? N : 0};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool aligned = ldx % 8 == 0 && x_group_stride % 8 == 0 && w_group_stride % 8 == 0 && ldo % 2 == 0 && o_group_stride % 2 == 0 &&
                        reinterpret_cast<uintptr_t>(d_x) % 16 == 0 && reinterpret_cast<uintptr_t>(d_w) % 16 == 0 &&
@@ -856,7 +915,7 @@ int vb_linear(void* d_out, const void* d_x, const void* d_w, int T, int N, int K
   VB_CHECK_ARG(epilogue >= 0 && epilogue <= 4, "vb_linear: epilogue %d", epilogue);
   VB_CHECK_ARG(groups >= 1 && (groups == 1 || d_row_off), "vb_linear: grouped launches need row offsets");
   if (T <= 0) return 0;
-  LinearParams p{d_out, d_x, d_w, d_row_off, d_gather, T, N, K, ldx, ldo, epilogue, w_group_stride, alpha, 0, 0, nullptr, 0,
+  LinearParams p{d_out, d_x, d_w, d_row_off, d_gather, T, N, K, ldx, ldo, epilogue, w_group_stride, alpha, 0, 0, nullptr, 0, 0,
                  glu_limit, glu_slope};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // in_dtype: 0 = bf16 activations and weights, 1 = fp32 both; out_dtype likewise

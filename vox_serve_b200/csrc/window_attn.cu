@@ -273,22 +273,24 @@ __global__ void __launch_bounds__(LR_THREADS) latent_rope_append_kernel(LatentRo
   if (p.stage_hi > 0) row = stage_row(row, p.stage_lo, p.stage_hi, tail_sm);
   const float* c = row + p.c_off;
   const float* cs = p.cs ? p.cs + t * 2 * p.half : nullptr;
-  float sc = 0.f;
-  for (int i = threadIdx.x; i < p.kv_rank; i += LR_THREADS) sc = fmaf(c[i], c[i], sc);
-  sc = warp_sum(sc);
-  if (lane == 0) red[warp] = sc;
-  __syncthreads();
-  sc = 0.f;
-#pragma unroll
-  for (int i = 0; i < LR_THREADS / 32; ++i) sc += red[i];
-  const float rc = 1.f / sqrtf(sc / p.kv_rank + p.eps);
-  const int b = p.row_req[t], ps = p.pos[t];
-  const size_t tok = static_cast<size_t>(p.page_indices[p.page_indptr[b] + ps / p.page_size]) * p.page_size + ps % p.page_size;
   const int ldc = p.kv_rank + p.rot;
-  CT* co = static_cast<CT*>(p.cache) + tok * ldc;
-  for (int i = threadIdx.x; i < p.kv_rank; i += LR_THREADS) co[i] = wa_from_f<CT>(c[i] * rc * p.wc[i]);
-  for (int i = threadIdx.x; i < p.rot; i += LR_THREADS)
-    co[p.kv_rank + i] = wa_from_f<CT>(rotated_value(c + p.kv_rank, nullptr, 1.f, cs, p.half, p.layout, i));
+  if (p.cache) {          // (a layer that reads another layer's cached rows has no latent of its own: queries only)
+    float sc = 0.f;
+    for (int i = threadIdx.x; i < p.kv_rank; i += LR_THREADS) sc = fmaf(c[i], c[i], sc);
+    sc = warp_sum(sc);
+    if (lane == 0) red[warp] = sc;
+    __syncthreads();
+    sc = 0.f;
+#pragma unroll
+    for (int i = 0; i < LR_THREADS / 32; ++i) sc += red[i];
+    const float rc = 1.f / sqrtf(sc / p.kv_rank + p.eps);
+    const int b = p.row_req[t], ps = p.pos[t];
+    const size_t tok = static_cast<size_t>(p.page_indices[p.page_indptr[b] + ps / p.page_size]) * p.page_size + ps % p.page_size;
+    CT* co = static_cast<CT*>(p.cache) + tok * ldc;
+    for (int i = threadIdx.x; i < p.kv_rank; i += LR_THREADS) co[i] = wa_from_f<CT>(c[i] * rc * p.wc[i]);
+    for (int i = threadIdx.x; i < p.rot; i += LR_THREADS)
+      co[p.kv_rank + i] = wa_from_f<CT>(rotated_value(c + p.kv_rank, nullptr, 1.f, cs, p.half, p.layout, i));
+  }
   const int dq = p.dim + p.rot;
   CT* qo = static_cast<CT*>(p.q_out) + t * p.H * p.dim;
   CT* ql = static_cast<CT*>(p.q_lat) + t * p.H * ldc;
@@ -1028,18 +1030,21 @@ int vb_latent_rope_append(const float* d_proj, int ldp, int q_off, int c_off, in
                           const float* d_wc, const float* d_cs, int half, int layout, void* d_q_out, void* d_q_lat,
                           void* d_cache, const int32_t* d_row_req, const int32_t* d_pos, const int32_t* d_page_indptr,
                           const int32_t* d_page_indices, int page_size, int T, float eps, int dtype, void* stream) {
-  VB_CHECK_ARG(d_proj && d_wc && d_q_out && d_q_lat && d_cache && d_row_req && d_pos && d_page_indptr && d_page_indices,
+  // d_cache == nullptr: the layer reads rows that another layer cached; only its queries are laid out (c_off, d_wc unused)
+  VB_CHECK_ARG(d_proj && d_q_out && d_q_lat && d_row_req && d_pos && d_page_indptr && d_page_indices && (!d_cache || d_wc),
                "vb_latent_rope_append: null pointer");
+  const int c_cols = d_cache ? kv_rank + rot : 0;
+  if (!d_cache) c_off = q_off;
   VB_CHECK_ARG(H > 0 && dim >= 0 && rot >= 0 && dim + rot > 0 && kv_rank > 0 && page_size > 0 && half >= 0 && 2 * half <= rot &&
                (layout == 0 || layout == 1) && q_off >= 0 && c_off >= 0 && q_off + H * (dim + rot) <= ldp &&
-               c_off + kv_rank + rot <= ldp, "vb_latent_rope_append: bad sizes H=%d dim=%d rot=%d kv_rank=%d rotated=%d",
+               c_off + c_cols <= ldp, "vb_latent_rope_append: bad sizes H=%d dim=%d rot=%d kv_rank=%d rotated=%d",
                H, dim, rot, kv_rank, 2 * half);
   if (T <= 0) return 0;
   LatentRopeTailParams p{d_proj, ldp, q_off, c_off, H, dim, rot, kv_rank, d_wc, half > 0 ? d_cs : nullptr, half, layout,
                          d_q_out, d_q_lat, d_cache, d_row_req, d_pos, d_page_indptr, d_page_indices, page_size, eps, 0, 0};
-  const int lo = min(q_off, c_off), hi = max(q_off + H * (dim + rot), c_off + kv_rank + rot);
+  const int lo = min(q_off, c_off), hi = max(q_off + H * (dim + rot), c_off + c_cols);
   size_t smem = 0;
-  if (hi - lo == H * (dim + rot) + kv_rank + rot && static_cast<size_t>(hi - lo) * sizeof(float) <= static_cast<size_t>(VB_MAX_DYN_SMEM)) {
+  if (hi - lo == H * (dim + rot) + c_cols && static_cast<size_t>(hi - lo) * sizeof(float) <= static_cast<size_t>(VB_MAX_DYN_SMEM)) {
     p.stage_lo = lo; p.stage_hi = hi;
     smem = static_cast<size_t>(hi - lo) * sizeof(float);
   }

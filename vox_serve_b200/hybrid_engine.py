@@ -135,6 +135,56 @@ class LatentAttentionConfig:
     rot_dim: int = 0
     rotary: Optional[RotaryConfig] = None
     head_gate: bool = True
+    window: int = 0                       # > 0: position i sees the keys j with 0 <= i - j < window
+    value_gate: bool = False              # the concatenated heads times sigmoid(W_g h), one gate per output value
+
+
+@dataclass
+class PooledSigmoidAttentionConfig:
+    """Grouped-head attention without rotation whose weights are sigmoid(score + bias of the head), not normalised over the
+    keys.  q, k, v pass a short causal convolution (conv taps; 0 / 1: none) right after their projection; q and k are then
+    RMS-normed over their WHOLE projection (all heads at once, one weight per coordinate).  Scores are soft-capped
+    (softcap * tanh(score / softcap); 0: no cap).  A position sees the tokens of its window and, with pool = P > 0, one mean
+    key / value per block of P positions that lies wholly before the window."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    window: int = 0
+    pool: int = 0
+    softcap: float = 0.0
+    conv: int = 0
+    qk_norm: bool = True
+
+
+@dataclass
+class SelectiveScanConfig:
+    """Mamba-form recurrence: [x | z] = W_in h; x through a causal convolution (conv taps, with bias) and silu; [dt | B | C] =
+    W_x x with dt of dt_rank dims, dt <- softplus(W_dt dt + b); S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n over an fp32
+    state [inner, state] per request; y_c = sum_n S[c, n] C_n + D_c x_c; output W_o (y * silu(z))."""
+    inner: int
+    state: int
+    dt_rank: int
+    conv: int
+
+
+@dataclass
+class MixerPairConfig:
+    """Two mixers side by side on the same input; the result is left_scale * left + right_scale * right."""
+    left: PooledSigmoidAttentionConfig
+    right: SelectiveScanConfig
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+
+
+@dataclass
+class PairEmbedConfig:
+    """A second embedding of (previous token, token) pairs: row (prev * mul_prev + token * mul_cur) mod buckets of a table of
+    buckets + 1 rows, whose last row serves a sequence's first token."""
+    buckets: int
+    mul_prev: int
+    mul_cur: int
 
 
 @dataclass
@@ -183,17 +233,23 @@ class MoEConfig:
     top: int
     ff: int
     shared_ff: int = 0                    # 0: no shared expert
-    act: str = "silu_glu"                 # "silu_glu": down(silu(gate h) * up h); else down(act(up h)) as DenseMLPConfig.act
+    act: str = "silu_glu"                 # "silu_glu": down(silu(gate h) * up h); "clamped_glu": down(g sigmoid(slope g) (u + 1))
+    #                                       with g = min(gate h, limit), u = clamp(up h, +-limit); else down(act(up h)) as
+    #                                       DenseMLPConfig.act
     router: str = "softmax"               # "softmax": top logits, softmax over the chosen.  "sigmoid": sigmoid scores, chosen
-    #                                       by score + correction within the kept groups, weights = chosen scores / their sum
-    groups: int = 0                       # sigmoid router: experts form this many groups of neighbours (0 / 1: one pool)
+    #                                       by score + correction within the kept groups, weights = chosen scores / their sum.
+    #                                       "softmax_all": scores = softmax over ALL experts, the largest within the kept
+    #                                       groups chosen, weights = the chosen scores as they are
+    groups: int = 0                       # group routers: experts form this many groups of neighbours (0 / 1: one pool)
     groups_keep: int = 0                  # ... of which the best this many stay eligible
     shared_gate: bool = False             # the shared expert's output times sigmoid(w_sg . h)
+    limit: float = 0.0                    # "clamped_glu"
+    slope: float = 1.702
 
 
 @dataclass
 class HybridLayerConfig:
-    kind: str                             # "attention" | "lightning" | "latent" | "diff_attention" | "mingru"
+    kind: str                             # "attention" | "lightning" | "latent" | "diff_attention" | "mingru" | "mixer_pair"
     mixer: Any
     mlp: Any = None                       # MoEConfig | DenseMLPConfig | GluMLPConfig | None
 
@@ -207,7 +263,10 @@ class HybridConfig:
     layers: List[HybridLayerConfig]
     block: str = "sequential"             # "sequential": x += LN(mixer(LN x)); x += LN(ff(LN x)).  "parallel": x += m * (mixer(n1 x) + ff(n2 x))
     #                                       "gated": pre-norm, x += sigmoid(W_r h + b) * sublayer(h) with h = norm(x), mixer then ff
-    norm: str = "layernorm"               # "layernorm" (weight and bias) | "rmsnorm" (weight) | "rmsnorm_scalar" (one number)
+    #                                       "post": norm on the sublayer's output only, x += norm(sublayer(x)); the sublayers
+    #                                       read the stream itself (the mixer through the input convolution, if any)
+    norm: str = "layernorm"               # "layernorm" (weight and bias) | "rmsnorm" (weight) | "rmsnorm_scalar" (one number) |
+    #                                       "rmsnorm_offset" (the stored weight is an offset from one: x / rms * (1 + w))
     residual_mult: float = 1.0            # m of the parallel form
     positions: int = 0                    # rows of the learned position table added to the embedding (0: none)
     side_dim: int = 0                     # per-token side input of every block (parallel form): dims per layer (0: none)
@@ -218,6 +277,10 @@ class HybridConfig:
     loop_start: int = 0
     loop_stop: int = 0
     loop_times: int = 1
+    tied_head: bool = False               # the output head is the embedding table itself (unscaled); no "head" tensor
+    pair_embed: Optional[PairEmbedConfig] = None   # a hashed (previous token, token) embedding added to the token's
+    input_conv: int = 0                   # "post" blocks: the mixer reads h + conv(h), a causal convolution of this many taps
+    #                                       over time on every channel of the stream (0: it reads h)
 
     def runs(self) -> List[Tuple[int, bool]]:
         """(layer index, does a repeated pass start here) for every layer run in order.  Caches and states are kept per run."""
@@ -318,15 +381,23 @@ class HybridWeights:
         elif cfg.norm == "rmsnorm_scalar":
             def norm(name):                                        # noqa: F811  (one number, kept as a constant vector)
                 return vec(name).reshape(1).expand(cfg.width).contiguous(), None
+        elif cfg.norm == "rmsnorm_offset":
+            def norm(name):                                        # noqa: F811  (stored around zero: the weight is 1 + w, in fp32)
+                return (vec(name) + 1.0).contiguous(), None
         self._gate_up = gate_up
         self.embed = mat("embed")
-        self.head = dense(mat("head"))
+        head_name = "embed" if cfg.tied_head else "head"          # (tied: the table itself, whatever scale the embedding takes)
+        self.head = dense(mat(head_name))
         self.final_norm = norm("final.norm")
         # the tcgen05 kernel has no output scale: logit_scale is folded into the final norm's weight and bias there
         self.final_norm_scaled = tuple(t * cfg.logit_scale if t is not None else None for t in self.final_norm)
-        if tuple(self.embed.shape) != (cfg.vocab, cfg.width) or tuple(sd["head"].shape) != (cfg.vocab, cfg.width):
+        if tuple(self.embed.shape) != (cfg.vocab, cfg.width) or tuple(sd[head_name].shape) != (cfg.vocab, cfg.width):
             raise VoxB200Error("embed / head shapes do not match the configuration")
-        self.pos = self.side_embed = None
+        self.pos = self.side_embed = self.pair_table = None
+        if cfg.pair_embed is not None:
+            self.pair_table = mat("bigram")
+            if tuple(self.pair_table.shape) != (cfg.pair_embed.buckets + 1, cfg.width):
+                raise VoxB200Error("pair embedding shape does not match the configuration")
         if cfg.positions:
             self.pos = mat("pos")
             if tuple(self.pos.shape) != (cfg.positions, cfg.width):
@@ -341,6 +412,9 @@ class HybridWeights:
             m = L.mixer
             if cfg.block == "gated":
                 self.layers.append(self._load_gated_layer(sd, p, i, L, norm))
+                continue
+            if cfg.block == "post":
+                self.layers.append(self._load_post_layer(sd, p, i, L, norm))
                 continue
             if cfg.block == "parallel":
                 w: Dict[str, Any] = {"norm1": vec(p + "norm1")}
@@ -381,35 +455,125 @@ class HybridWeights:
                 f = L.mlp
                 if cfg.block != "parallel":
                     w["norm2"], w["norm2b"] = norm(p + "norm2"), norm(p + "norm2b")
-                w["router"] = vec(p + "mlp.router")
-                w["router_b"] = vec(p + "mlp.router.b") if (p + "mlp.router.b") in sd else None
-                n_all = f.experts * f.ff + f.shared_ff
-                if self.tensor_core and cfg.width % 8 == 0 and n_all % 8 == 0 and f.experts <= self.DENSE_MOE_MAX_RATIO * f.top:
-                    # dense form (vb_moe_scale_dense): all experts and the shared expert as one gate/up and one down matrix
-                    names = [f"e{e}" for e in range(f.experts)] + (["shared"] if f.shared_ff else [])
-                    gate = torch.cat([mat(p + f"mlp.{n}.gate") for n in names], 0)
-                    up = torch.cat([mat(p + f"mlp.{n}.up") for n in names], 0)
-                    # a gate/up tile height that divides every expert keeps tiles from straddling experts: the stacked
-                    # buffer is then also the per-expert buffers one after the other, which the grouped form indexes
-                    fit = [hh for hh in (64, 48, 32, 16) if f.ff % hh == 0 and f.shared_ff % hh == 0]
-                    half = fit[0] if fit else ops.gate_up_tile_half(n_all)
-                    w["gu_all"] = ops.pack_weight(ops.interleave_gate_up(gate, up, half), 2 * half)
-                    del gate, up
-                    w["down_all"] = ops.pack_weight(torch.cat([mat(p + f"mlp.{n}.down") for n in names], 1).contiguous(), 128)
-                    if fit and f.ff % 64 == 0:
-                        gb = ops.weight_tiles_bytes(2 * f.ff, cfg.width, 2 * half)
-                        w["grouped"] = {"group_bytes": gb, "kb_total": (n_all + 63) // 64, "group_kb": f.ff // 64}
-                        if f.shared_ff:
-                            w["s_gu_view"] = ops.PackedWeight(w["gu_all"].data[f.experts * gb:], 2 * f.shared_ff, cfg.width,
-                                                              2 * half)
-                else:
-                    w["gu"] = torch.stack([mat(p + f"mlp.e{e}.gate", p + f"mlp.e{e}.up") for e in range(f.experts)]).contiguous()
-                    w["down"] = torch.stack([mat(p + f"mlp.e{e}.down") for e in range(f.experts)]).contiguous()
-                    if f.shared_ff:
-                        w["s_gu"] = gate_up(p + "mlp.shared.gate", p + "mlp.shared.up")
-                        w["s_down"] = dense(mat(p + "mlp.shared.down"))
+                self._load_gated_moe(sd, p, f, w)
             self.layers.append(w)
         del self._mat, self._vec, self._dense, self._gate_up
+
+    def _load_gated_moe(self, sd, p: str, f: "MoEConfig", w: Dict[str, Any]) -> None:
+        """Experts with a gate and an up matrix (``l<i>.mlp.{router[, router.b], e<j>.{gate,up,down}[, shared.{gate,up,down}]}``):
+        on tensor-core projections all experts and the shared expert stacked into ONE interleaved gate/up matrix (along N) and
+        ONE down matrix (along K), with the per-expert offsets of the grouped form where tiles do not straddle experts;
+        otherwise [E, ...] stacks for the grouped linear kernel."""
+        mat, vec, dense, gate_up, cfg = self._mat, self._vec, self._dense, self._gate_up, self.cfg
+        w["router"] = vec(p + "mlp.router")
+        w["router_b"] = vec(p + "mlp.router.b") if (p + "mlp.router.b") in sd else None
+        n_all = f.experts * f.ff + f.shared_ff
+        if self.tensor_core and cfg.width % 8 == 0 and n_all % 8 == 0 and f.experts <= self.DENSE_MOE_MAX_RATIO * f.top:
+            # dense form (vb_moe_scale_dense): all experts and the shared expert as one gate/up and one down matrix
+            names = [f"e{e}" for e in range(f.experts)] + (["shared"] if f.shared_ff else [])
+            gate = torch.cat([mat(p + f"mlp.{n}.gate") for n in names], 0)
+            up = torch.cat([mat(p + f"mlp.{n}.up") for n in names], 0)
+            # a gate/up tile height that divides every expert keeps tiles from straddling experts: the stacked
+            # buffer is then also the per-expert buffers one after the other, which the grouped form indexes
+            fit = [hh for hh in (64, 48, 32, 16) if f.ff % hh == 0 and f.shared_ff % hh == 0]
+            half = fit[0] if fit else ops.gate_up_tile_half(n_all)
+            w["gu_all"] = ops.pack_weight(ops.interleave_gate_up(gate, up, half), 2 * half)
+            del gate, up
+            w["down_all"] = ops.pack_weight(torch.cat([mat(p + f"mlp.{n}.down") for n in names], 1).contiguous(), 128)
+            if fit and f.ff % 64 == 0:
+                gb = ops.weight_tiles_bytes(2 * f.ff, cfg.width, 2 * half)
+                w["grouped"] = {"group_bytes": gb, "kb_total": (n_all + 63) // 64, "group_kb": f.ff // 64}
+                if f.shared_ff:
+                    w["s_gu_view"] = ops.PackedWeight(w["gu_all"].data[f.experts * gb:], 2 * f.shared_ff, cfg.width,
+                                                      2 * half)
+        else:
+            w["gu"] = torch.stack([mat(p + f"mlp.e{e}.gate", p + f"mlp.e{e}.up") for e in range(f.experts)]).contiguous()
+            w["down"] = torch.stack([mat(p + f"mlp.e{e}.down") for e in range(f.experts)]).contiguous()
+            if f.shared_ff:
+                w["s_gu"] = gate_up(p + "mlp.shared.gate", p + "mlp.shared.up")
+                w["s_down"] = dense(mat(p + "mlp.shared.down"))
+
+    def _load_post_layer(self, sd, p: str, i: int, L: "HybridLayerConfig", norm) -> Dict[str, Any]:
+        """A layer of a stack that norms sublayer OUTPUTS only: ``l<i>.norm1`` / ``norm2``, ``l<i>.canon1`` (the input
+        convolution [width, taps]), ``l<i>.mix.*``, ``l<i>.mlp.{router, e<j>.{gate,up,down}}``.
+          latent attention with direct queries: in = q | dkv | g (no dkv in a layer that reads another layer's cached rows);
+            uk per head transposed, uv per head
+          mixer pair: in = left.q | left.k | left.v | right.in -- ONE projection for both mixers; the three short convolutions
+            of the left mixer stacked into one [nq + nk + nv, taps]; A = -exp(A_log) formed here in fp32; o = [left.o | right.o]
+            side by side along K, so ONE output projection sums both mixers (their scales go on its input)."""
+        mat, vec, dense, cfg, W, m = self._mat, self._vec, self._dense, self.cfg, self.cfg.width, L.mixer
+        w: Dict[str, Any] = {"norm1": norm(p + "norm1")[0]}
+        if cfg.input_conv:
+            w["canon"] = vec(p + "canon1")
+            if tuple(w["canon"].shape) != (W, cfg.input_conv):
+                raise VoxB200Error(f"layer {i}: input convolution shape does not match the configuration")
+        if L.kind == "latent":
+            own = m.kv_from is None
+            if m.q_rank or m.head_gate:
+                raise VoxB200Error(f"layer {i}: post-norm blocks take latent attention with direct queries and no per-head gate")
+            if not own:
+                src = cfg.layers[m.kv_from] if 0 <= m.kv_from < i else None
+                if (src is None or src.kind != "latent" or src.mixer.kv_from is not None or src.mixer.kv_rank != m.kv_rank or
+                        src.mixer.rot_dim != m.rot_dim or (src.mixer.rotary.key() if src.mixer.rotary else None) !=
+                        (m.rotary.key() if m.rotary else None)):
+                    raise VoxB200Error(f"layer {i}: kv_from {m.kv_from} must name an earlier latent-attention layer that projects "
+                                       "its own latents, of the same rank, rotated part and rotation")
+            dq = m.dim + m.rot_dim
+            parts = [mat(p + "mix.q")] + ([mat(p + "mix.dkv")] if own else []) + ([mat(p + "mix.g")] if m.value_gate else [])
+            uk, uv, o = mat(p + "mix.uk"), mat(p + "mix.uv"), mat(p + "mix.o")
+            if (tuple(parts[0].shape) != (m.heads * dq, W) or (own and tuple(parts[1].shape) != (m.kv_rank + m.rot_dim, W)) or
+                    (m.value_gate and tuple(parts[-1].shape) != (m.heads * m.vdim, W)) or
+                    tuple(uk.shape) != (m.heads * m.dim, m.kv_rank) or tuple(uv.shape) != (m.heads * m.vdim, m.kv_rank) or
+                    tuple(o.shape) != (W, m.heads * m.vdim)):
+                raise VoxB200Error(f"layer {i}: latent attention shapes do not match the configuration")
+            w["in"] = dense(torch.cat(parts, 0).contiguous())
+            if own:
+                w["dkv_norm"] = vec(p + "mix.dkv.norm")
+            w["uk_t"] = uk.view(m.heads, m.dim, m.kv_rank).transpose(1, 2).contiguous()
+            w["uv"] = uv.view(m.heads, m.vdim, m.kv_rank).contiguous()
+            w["o"] = dense(o)
+        elif L.kind == "mixer_pair":
+            a, r = m.left, m.right
+            nq, nk, nv = a.heads * a.dim, a.kv_heads * a.dim, a.kv_heads * a.vdim
+            lp, rp = p + "mix.left.", p + "mix.right."
+            q, k, v, xin = mat(lp + "q"), mat(lp + "k"), mat(lp + "v"), mat(rp + "in")
+            lo, ro = mat(lp + "o"), mat(rp + "o")
+            xp, dtp = mat(rp + "x"), mat(rp + "dt")
+            if (tuple(q.shape) != (nq, W) or tuple(k.shape) != (nk, W) or tuple(v.shape) != (nv, W) or
+                    tuple(lo.shape) != (W, a.heads * a.vdim)):
+                raise VoxB200Error(f"layer {i}: attention shapes do not match the configuration")
+            if (tuple(xin.shape) != (2 * r.inner, W) or tuple(ro.shape) != (W, r.inner) or
+                    tuple(xp.shape) != (r.dt_rank + 2 * r.state, r.inner) or tuple(dtp.shape) != (r.inner, r.dt_rank) or
+                    tuple(sd[rp + "A_log"].shape) != (r.inner, r.state)):
+                raise VoxB200Error(f"layer {i}: selective-scan shapes do not match the configuration")
+            w["in"] = dense(torch.cat([q, k, v, xin], 0).contiguous())
+            if a.conv > 1:
+                w["qkv_conv"] = torch.cat([vec(lp + n + ".conv") for n in ("q", "k", "v")], 0).contiguous()
+                if tuple(w["qkv_conv"].shape) != (nq + nk + nv, a.conv):
+                    raise VoxB200Error(f"layer {i}: short convolution shapes do not match the configuration")
+            if a.qk_norm:
+                w["q_norm"], w["k_norm"] = vec(lp + "q.norm"), vec(lp + "k.norm")
+            w["head_bias"] = vec(lp + "pb")
+            if w["head_bias"].numel() != a.heads:
+                raise VoxB200Error(f"layer {i}: one score bias per head")
+            w["x_conv"], w["x_conv_b"] = vec(rp + "conv"), vec(rp + "conv.b")
+            if tuple(w["x_conv"].shape) != (r.inner, r.conv):
+                raise VoxB200Error(f"layer {i}: selective-scan convolution shape does not match the configuration")
+            w["x_proj"], w["dt_proj"], w["dt_b"] = dense(xp), dense(dtp), vec(rp + "dt.b")
+            w["A"] = (-torch.exp(vec(rp + "A_log"))).contiguous()
+            w["D"] = vec(rp + "D")
+            w["o"] = dense(torch.cat([lo, ro], 1).contiguous())
+        else:
+            raise VoxB200Error(f"layer {i}: mixer '{L.kind}' is not available in post-norm blocks")
+        f = L.mlp
+        if f is not None:
+            if not isinstance(f, MoEConfig) or f.act not in ("silu_glu", "clamped_glu"):
+                raise VoxB200Error(f"layer {i}: post-norm blocks take a mixture of gated experts")
+            w["norm2"] = norm(p + "norm2")[0]
+            self._load_gated_moe(sd, p, f, w)
+            if tuple(w["router"].shape) != (f.experts, W):
+                raise VoxB200Error(f"layer {i}: router shape does not match the configuration")
+        return w
 
     def _load_gated_layer(self, sd, p: str, i: int, L: "HybridLayerConfig", norm) -> Dict[str, Any]:
         """A pre-norm layer with gated residuals: ``l<i>.norm1`` / ``norm2``, ``l<i>.rg1[.b]`` / ``rg2[.b]`` (the gates of the
@@ -552,7 +716,8 @@ class HybridWeights:
             elif isinstance(o, dict):
                 for x in o.values():
                     walk(x)
-        walk([self.embed, self.head, self.final_norm, self.pos, self.side_embed,
+        walk([self.embed, None if self.cfg.tied_head and self.head is self.embed else self.head, self.final_norm, self.pos,
+              self.side_embed, self.pair_table,
               [{k: v for k, v in L.items() if k not in ("s_gu_view", "s_up_view")} for L in self.layers]])   # (views of other entries)
         return n
 
@@ -565,7 +730,10 @@ class HybridCache:
     one page table: page p of every layer belongs to the same request); per latent-attention layer that projects its own
     latents ONE tensor [pages, page, 1, kv_rank (+ rot_dim)] that is both K and V (a layer reading another layer's latents aliases
     that layer's tensor); per attention layer with two score maps K [pages, page, 2 G, dim] and V [pages, page, G, vdim];
-    per linear-attention layer a state [slots, H, dim, vdim] and per minGRU layer a state [slots, width] in fp32.  A layer
+    per linear-attention layer a state [slots, H, dim, vdim] and per minGRU layer a state [slots, width] in fp32; per mixer
+    pair K / V pages of its attention, fp32 pooled blocks [pages, ceil(page / pool), G, dim / vdim], the scan's state
+    [slots, inner, N] and the last inputs of its short convolutions [slots, taps - 1, channels]; per layer of a stack with an
+    input convolution its last inputs [slots, taps - 1, width]; with a token-pair embedding the last token of every slot.  A layer
     that a loop runs several times has one of these per pass.  Pages and slots are handed out by the worker; a slot's state is treated as zero by
     the kernels when its request starts at position 0, so nothing is cleared on reuse."""
 
@@ -574,6 +742,11 @@ class HybridCache:
         self.k: Dict[int, torch.Tensor] = {}
         self.v: Dict[int, torch.Tensor] = {}
         self.state: Dict[int, torch.Tensor] = {}
+        self.k_pool: Dict[int, torch.Tensor] = {}        # fp32 means of completed key / value blocks (pooled-window attention)
+        self.v_pool: Dict[int, torch.Tensor] = {}
+        self.conv: Dict[Tuple[int, str], torch.Tensor] = {}     # (run, which) -> the last taps - 1 inputs of a short convolution
+        # the last token of every slot's request (stacks with a token-pair embedding)
+        self.prev_tok = torch.zeros(num_slots, dtype=I32, device=device) if cfg.pair_embed is not None else None
         # one entry per layer RUN (a layer inside a loop runs several times, each pass with a cache or state of its own);
         # without a loop the run index is the layer index
         for i, (li, _) in enumerate(cfg.runs()):
@@ -592,11 +765,27 @@ class HybridCache:
                     self.k[i] = self.v[i] = self.k[m.kv_from]
             elif L.kind == "mingru":
                 self.state[i] = torch.zeros(num_slots, m.width, dtype=F32, device=device)
+            elif L.kind == "mixer_pair":
+                a, r = m.left, m.right
+                self.k[i] = torch.zeros(num_pages, page_size, a.kv_heads, a.dim, dtype=dtype, device=device)
+                self.v[i] = torch.zeros(num_pages, page_size, a.kv_heads, a.vdim, dtype=dtype, device=device)
+                if a.pool > 0:
+                    per_page = (page_size + a.pool - 1) // a.pool
+                    self.k_pool[i] = torch.zeros(num_pages, per_page, a.kv_heads, a.dim, dtype=F32, device=device)
+                    self.v_pool[i] = torch.zeros(num_pages, per_page, a.kv_heads, a.vdim, dtype=F32, device=device)
+                if a.conv > 1:
+                    n = a.heads * a.dim + a.kv_heads * (a.dim + a.vdim)
+                    self.conv[(i, "qkv")] = torch.zeros(num_slots, a.conv - 1, n, dtype=F32, device=device)
+                self.conv[(i, "x")] = torch.zeros(num_slots, max(r.conv - 1, 1), r.inner, dtype=F32, device=device)
+                self.state[i] = torch.zeros(num_slots, r.inner, r.state, dtype=F32, device=device)
             else:
                 self.state[i] = torch.zeros(num_slots, m.heads, m.dim, m.vdim, dtype=F32, device=device)
+            if cfg.block == "post" and cfg.input_conv > 1:
+                self.conv[(i, "in")] = torch.zeros(num_slots, cfg.input_conv - 1, cfg.width, dtype=F32, device=device)
 
     def nbytes(self) -> int:
-        seen = {t.data_ptr(): t for d in (self.k, self.v, self.state) for t in d.values()}      # (aliases count once)
+        seen = {t.data_ptr(): t for d in (self.k, self.v, self.state, self.k_pool, self.v_pool, self.conv)
+                for t in d.values()}      # (aliases count once)
         return sum(t.numel() * t.element_size() for t in seen.values())
 
 
@@ -636,15 +825,19 @@ class HybridEngine:
         lat = [L.mixer for L in cfg.layers if L.kind == "latent"]
         dif = [L.mixer for L in cfg.layers if L.kind == "diff_attention"]
         gru = [L.mixer for L in cfg.layers if L.kind == "mingru"]
+        par = [L.mixer for L in cfg.layers if L.kind == "mixer_pair"]
         moe = [L.mlp for L in cfg.layers if isinstance(L.mlp, MoEConfig)]
         dmlp = [L.mlp for L in cfg.layers if isinstance(L.mlp, (DenseMLPConfig, GluMLPConfig))]
         gated = W if cfg.block == "gated" else 0          # the residual gate's columns ride on the mixer's input projection
         p_att = [m.heads * m.dim + m.kv_heads * (m.dim + m.vdim) + m.heads * m.vdim for m in att]
         p_lin = [2 * m.heads * (m.dim + m.vdim) for m in lin]
-        p_lat = [(m.q_rank if m.q_rank else m.heads * (m.dim + m.rot_dim)) + m.kv_rank + m.rot_dim + m.heads + gated for m in lat]
+        p_lat = [(m.q_rank if m.q_rank else m.heads * (m.dim + m.rot_dim)) + m.kv_rank + m.rot_dim +
+                 (m.heads * m.vdim if m.value_gate else m.heads) + gated for m in lat]
+        p_par = [m.left.heads * m.left.dim + m.left.kv_heads * (m.left.dim + m.left.vdim) + 2 * m.right.inner for m in par]
         p_dif = [2 * (m.heads + m.kv_heads) * m.dim + m.kv_heads * m.vdim + m.heads * m.vdim + gated for m in dif]
         p_gru = [3 * m.width + gated for m in gru]
-        hv = max([m.heads * m.vdim for m in att + lin + lat + dif] + [m.width for m in gru] + [1])
+        hv = max([m.heads * m.vdim for m in att + lin + lat + dif] + [m.width for m in gru] +
+                 [m.left.heads * m.left.vdim + m.right.inner for m in par] + [1])
         for m in lat:
             if m.kv_rank > 256:
                 raise VoxB200Error(f"latent attention: kv_rank {m.kv_rank} exceeds the 256 dims the attention kernels take per head")
@@ -657,9 +850,33 @@ class HybridEngine:
         self.x = torch.zeros(R, W, dtype=F32, device=dev)              # residual stream
         self.h = torch.zeros(R, W, dtype=CT, device=dev)               # normed input of the running sublayer
         self.y = torch.zeros(R, W, dtype=F32, device=dev)              # sublayer output
-        self.proj = torch.zeros(R * max(p_att + p_lin + p_lat + p_dif + p_gru + [1]), dtype=F32, device=dev)
-        self.q = torch.zeros(R * max([m.heads * m.dim for m in att + lat] + [2 * m.heads * m.dim for m in dif] + [1]),
-                             dtype=CT, device=dev)
+        self.proj = torch.zeros(R * max(p_att + p_lin + p_lat + p_dif + p_gru + p_par + [1]), dtype=F32, device=dev)
+        self.q = torch.zeros(R * max([m.heads * m.dim for m in att + lat] + [2 * m.heads * m.dim for m in dif] +
+                                     [m.left.heads * m.left.dim for m in par] + [1]), dtype=CT, device=dev)
+        for m in par:
+            a = m.left
+            if a.heads % a.kv_heads or a.dim > 256 or a.vdim > 256:
+                raise VoxB200Error(f"attention: {a.heads} heads on {a.kv_heads} key/value heads of {a.dim} / {a.vdim} dims "
+                                   "(heads a multiple of key/value heads, at most 256 dims per head)")
+            if a.pool > 0 and a.window <= 0:
+                raise VoxB200Error("pooled blocks lie before a window: mask.pool needs mask.size")
+            if m.right.state > 256 or m.right.conv > 16 or a.conv > 16 or m.right.conv < 1:
+                raise VoxB200Error("selective scan: at most 256 states per channel, convolutions of 1 to 16 taps")
+        if par:
+            # the convolved q | k | v rows, and the scan's operands: x after its convolution (fp32 for the recurrence, compute
+            # type for the low-rank projection), [dt | B | C], dt's operand, the step sizes before their bias
+            self.proj2 = torch.zeros(R * max(m.left.heads * m.left.dim + m.left.kv_heads * (m.left.dim + m.left.vdim) for m in par),
+                                     dtype=F32, device=dev)
+            inner = max(m.right.inner for m in par)
+            self.scan_x = torch.zeros(R * inner, dtype=F32, device=dev)
+            self.scan_xc = torch.zeros(R * inner, dtype=CT, device=dev)
+            self.scan_low = torch.zeros(R * max(m.right.dt_rank + 2 * m.right.state for m in par), dtype=F32, device=dev)
+            self.scan_dtl = torch.zeros(R * max(m.right.dt_rank for m in par), dtype=CT, device=dev)
+            self.scan_dt = torch.zeros(R * inner, dtype=F32, device=dev)
+        if cfg.pair_embed is not None:
+            self.pair_rows = torch.zeros(R, dtype=I32, device=dev)
+        if cfg.input_conv > 16:
+            raise VoxB200Error("input convolution: at most 16 taps")
         if cfg.block == "gated":
             self.rg = torch.zeros(R, W, dtype=F32, device=dev)         # the feed-forward's residual gate before its sigmoid
             # the embedding output, added again before every repeated pass over the looped layers
@@ -692,11 +909,17 @@ class HybridEngine:
             n_t = max_rows // self.lin_tile_rows + max_out_rows + 1
             self.gru_scratch = torch.zeros(ops.mingru_scratch_floats(n_t, self.lin_tile_rows, max(m.width for m in gru))
                                            if dev.type == "cuda" else 1, dtype=F32, device=dev)
+        self.scan_scratch = None
+        if par and dev.type == "cuda":
+            n_t = max_rows // self.lin_tile_rows + cache.num_slots + 1
+            self.scan_scratch = torch.zeros(max(ops.selective_scan_scratch_floats(n_t, self.lin_tile_rows, m.right.inner, m.right.state)
+                                                for m in par), dtype=F32, device=dev)
         self.v_first = torch.zeros(R * max([m.kv_heads * m.vdim for m in att if m.v_mix] + [1]), dtype=F32, device=dev)
         # split-key scratch of the per-row attention kernel: steps of up to 256 rows, 8 splits
         self.attn_part = torch.zeros(256 * 8 * max([m.heads * (m.vdim + 2) for m in att] +
                                                    [2 * m.heads * (m.vdim + 2) for m in dif] +
-                                                   [m.heads * (m.kv_rank + 2) for m in lat] + [1]), dtype=F32, device=dev)
+                                                   [m.heads * (m.kv_rank + 2) for m in lat] +
+                                                   [m.left.heads * (m.left.vdim + 2) for m in par] + [1]), dtype=F32, device=dev)
         self.freqs: Dict[Tuple, torch.Tensor] = {}
         self.cs: Dict[Tuple, torch.Tensor] = {}
         self.cs_mult: Dict[Tuple, float] = {}
@@ -891,10 +1114,14 @@ class HybridEngine:
         T, W = s.T, self.cfg.width
         h = self.h[:T] if h is None else h
         out = self.y[:T] if out is None else out
-        if f.act != "silu_glu":
+        if f.act not in ("silu_glu", "clamped_glu"):
             return self._moe_plain(f, w, s, h, out)
         idx, wts = self.moe_idx[:T * f.top], self.moe_wts[:T * f.top]
-        ops.moe_route(h, w["router"], w["router_b"], f.top, idx, wts)
+        if f.router == "softmax_all":
+            ops.moe_route_groups(h, w["router"], f.top, idx, wts, f.groups, f.groups_keep, scores="softmax", group_rank="max")
+        else:
+            ops.moe_route(h, w["router"], w["router_b"], f.top, idx, wts)
+        glu = (f.limit, f.slope) if f.act == "clamped_glu" else None
         if "grouped" in w and T >= self.GROUPED_MIN_ROWS:
             # compute-bound steps: tokens sorted by expert into whole row tiles, each tile multiplied by its expert's slice of
             # the same packed buffers the dense form uses (tcgen05, gemm.cu), the shared expert as two plain projections
@@ -905,36 +1132,48 @@ class HybridEngine:
                           tile_group=self.moe_tile_group[:n_tiles])
             xs = ops.moe_gather_rows(h, self.moe_sorted, self.moe_xs[:rows * W].view(rows, W))
             act = self.moe_act[:rows * f.ff].view(rows, f.ff)
-            ops.gemm_grouped(xs, w["gu_all"], act, 2, 2 * f.ff, W, tt, self.moe_tile_group, group_bytes=g["group_bytes"],
-                             n_out=f.ff)
+            if glu:
+                ops.gemm_grouped_glu(xs, w["gu_all"], act, 2 * f.ff, W, tt, self.moe_tile_group, g["group_bytes"], *glu)
+            else:
+                ops.gemm_grouped(xs, w["gu_all"], act, 2, 2 * f.ff, W, tt, self.moe_tile_group, group_bytes=g["group_bytes"],
+                                 n_out=f.ff)
             eo = self.moe_out[:rows * W].view(rows, W)
             ops.gemm_grouped(act, w["down_all"], eo, 1, W, f.ff, tt, self.moe_tile_group, w_kb_stride=g["kb_total"],
                              group_kb=g["group_kb"])
             shared = None
             if f.shared_ff:
                 sa = self.s_act[:T * f.shared_ff].view(T, f.shared_ff)
-                ops.gemm(h, w["s_gu_view"], mode=2, out=sa, tile_rows=w["s_gu_view"].tile_rows, n_out=f.shared_ff)
+                if glu:
+                    ops.gemm_glu(h, w["s_gu_view"], sa, *glu)
+                else:
+                    ops.gemm(h, w["s_gu_view"], mode=2, out=sa, tile_rows=w["s_gu_view"].tile_rows, n_out=f.shared_ff)
                 shared = ops.gemm_grouped(sa, w["down_all"], self.s_out[:T], 1, W, f.shared_ff, ops.gemm_t_tile(T), None,
                                           w_kb_stride=g["kb_total"], kb_base=f.experts * g["group_kb"])
             return ops.moe_combine(eo, shared, wts, self.moe_pair_row, f.top, out)
         if "gu_all" in w:
             n_all = f.experts * f.ff + f.shared_ff
             act = self.moe_act[:T * n_all].view(T, n_all)
-            ops.gemm(h, w["gu_all"], mode=2, out=act, tile_rows=w["gu_all"].tile_rows, n_out=n_all)
+            if glu:
+                ops.gemm_glu(h, w["gu_all"], act, *glu)
+            else:
+                ops.gemm(h, w["gu_all"], mode=2, out=act, tile_rows=w["gu_all"].tile_rows, n_out=n_all)
             ops.moe_scale_dense(act, idx, wts, f.experts, f.ff, f.top)
             return self._proj(act, w["down_all"], out)
         ops.moe_group(idx, T, f.experts, f.top, self.moe_row_off, self.moe_sorted, self.moe_pair_row)
         act = self.moe_act[:T * f.top * f.ff].view(T * f.top, f.ff)
-        ops.linear(h, w["gu"], act, epilogue=1, row_off=self.moe_row_off, gather=self.moe_sorted, rows=T)
+        ops.linear(h, w["gu"], act, epilogue=1, row_off=self.moe_row_off, gather=self.moe_sorted, rows=T, glu=glu)
         eo = self.moe_out[:T * f.top * W].view(T * f.top, W)
         ops.linear(act, w["down"], eo, row_off=self.moe_row_off, rows=T)
         shared = None
         if f.shared_ff:
             sa = self.s_act[:T * f.shared_ff].view(T, f.shared_ff)
             if isinstance(w["s_gu"], ops.PackedWeight):
-                ops.gemm(h, w["s_gu"], mode=2, out=sa, tile_rows=w["s_gu"].tile_rows, n_out=f.shared_ff)
+                if glu:
+                    ops.gemm_glu(h, w["s_gu"], sa, *glu)
+                else:
+                    ops.gemm(h, w["s_gu"], mode=2, out=sa, tile_rows=w["s_gu"].tile_rows, n_out=f.shared_ff)
             else:
-                ops.linear(h, w["s_gu"], sa, epilogue=1)
+                ops.linear(h, w["s_gu"], sa, epilogue=1, glu=glu)
             shared = self._proj(sa, w["s_down"], self.s_out[:T])
         return ops.moe_combine(eo, shared, wts, self.moe_pair_row, f.top, out)
 
@@ -949,6 +1188,8 @@ class HybridEngine:
             return self._forward_parallel(s)
         if cfg.block == "gated":
             return self._forward_gated(s)
+        if cfg.block == "post":
+            return self._forward_post(s)
         x, h, y = self.x[:T], self.h[:T], self.y[:T]
         ops.embed_rows_f32(w.embed, s.ids, x, w.pos, s.pos if w.pos is not None else None, scale=cfg.embed_scale)
         for key, freq in self.freqs.items():
@@ -1079,25 +1320,33 @@ class HybridEngine:
             y = self._mingru(ci, m, lw, s, proj)
         return y, proj[:, P - W:]
 
-    def _latent_direct(self, ci: int, m: LatentAttentionConfig, w: Dict[str, Any], s: StepInputs, proj: torch.Tensor) -> torch.Tensor:
+    def _latent_direct(self, ci: int, m: LatentAttentionConfig, w: Dict[str, Any], s: StepInputs, proj: torch.Tensor,
+                       gate: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Latent attention whose queries come straight from the input and whose heads have a rotated part, in the absorbed
         form: a head's score q_u . (U_k c) + q_r . k_r equals [U_k^T q_u | q_r] . [c | k_r], so the cached rows [c | k_r]
         serve every head as ONE key head of kv_rank + rot_dim dims whose leading kv_rank dims are also the value; the
-        per-head value expansion U_v runs on the latent-space output."""
+        per-head value expansion U_v runs on the latent-space output.  proj: [queries | latent + rotated key part | ...]; a
+        layer with ``kv_from`` has no latent columns and attends over the rows the named layer cached (this step's included:
+        that layer ran before).  ``window`` limits the visible keys; ``gate`` (an fp32 view [T, H * vdim]): the heads' values
+        times its sigmoid."""
         T, H, R, D, Rd = s.T, m.heads, m.kv_rank, m.dim, m.rot_dim
         cache = self.cache.k[ci]
+        own = m.kv_from is None
         q = self.q[:T * H * D].view(T, H, D)
         q_lat = self.q_lat[:T * H * (R + Rd)].view(T, H, R + Rd)
         cs, half = (self.cs[m.rotary.key()], m.rotary.dims // 2) if (m.rotary is not None and Rd) else (None, 0)
-        ops.latent_rope_append(proj, 0, H * (D + Rd), H, D, Rd, R, w["dkv_norm"], cs, half,
-                               m.rotary.layout if m.rotary is not None else "interleaved", q, q_lat, cache, s.row_req, s.pos,
-                               s.page_indptr, s.page_indices, T, self.cfg.eps)
+        ops.latent_rope_append(proj, 0, H * (D + Rd), H, D, Rd, R, w.get("dkv_norm"), cs, half,
+                               m.rotary.layout if m.rotary is not None else "interleaved", q, q_lat, cache if own else None,
+                               s.row_req, s.pos, s.page_indptr, s.page_indices, T, self.cfg.eps)
         ops.linear_batched(q, w["uk_t"], q_lat[:, :, :R])
         o_lat = self.o_lat[:T * H * R].view(T, H * R)
-        self._run_attention(s, q_lat.view(T, H * (R + Rd)), cache, cache, o_lat, None, H, 1, R + Rd, R, 0, m.scale, head_rows=True,
-                            k_ld=R + Rd, v_ld=R + Rd)
+        self._run_attention(s, q_lat.view(T, H * (R + Rd)), cache, cache, o_lat, None, H, 1, R + Rd, R, m.window, m.scale,
+                            head_rows=True, k_ld=R + Rd, v_ld=R + Rd)
         out = self.mix_out[:T * H * m.vdim].view(T, H, m.vdim)
-        ops.linear_batched(o_lat.view(T, H, R), w["uv"], out)
+        if gate is not None:
+            ops.linear_batched_gated(o_lat.view(T, H, R), w["uv"], out, gate)
+        else:
+            ops.linear_batched(o_lat.view(T, H, R), w["uv"], out)
         return self._proj(out.view(T, H * m.vdim), w["o"], self.y[:T])
 
     def _diff_attention(self, ci: int, m: DiffAttentionConfig, w: Dict[str, Any], s: StepInputs, proj: torch.Tensor) -> torch.Tensor:
@@ -1143,3 +1392,95 @@ class HybridEngine:
             ops.linear(h, w["gu"], act, epilogue=1, glu=(f.limit, f.slope))
         r = self._proj(h, w["rg2"], self.rg[:T])
         return self._proj(act, w["down"], self.y[:T]), r
+
+    # ---- blocks that norm sublayer outputs only ------------------------------------------------------------------
+    def _forward_post(self, s: StepInputs) -> torch.Tensor:
+        """x += norm1(mixer(c(x))), then x += norm2(ff(x)): the sublayers read the stream itself -- the mixer through the input
+        convolution c(h) = h + conv(h) over time (state: a request's last taps - 1 rows of the stream, per layer), the
+        feed-forward as it is.  The embedding may add a hashed (previous token, token) row, whose previous token lives in the
+        request's slot between steps."""
+        cfg, w, T = self.cfg, self.w, s.T
+        x, h, eps = self.x[:T], self.h[:T], cfg.eps
+        rows = None
+        if cfg.pair_embed is not None:
+            pe = cfg.pair_embed
+            rows = ops.pair_hash_rows(self.pair_rows[:T], self.cache.prev_tok, s.ids, s.qo_indptr, s.row_req, s.pos, s.slots, T,
+                                      pe.buckets, pe.mul_prev, pe.mul_cur)
+        ops.embed_rows_f32(w.embed, s.ids, x, w.pair_table if rows is not None else None, rows, scale=cfg.embed_scale)
+        for key, freq in self.freqs.items():
+            ops.rotary_table(s.pos, freq, self.cs[key][:T], self.cs_mult[key])
+        for i, L in enumerate(cfg.layers):
+            lw = w.layers[i]
+            if cfg.input_conv:
+                ops.short_conv(x, lw["canon"], None, self.cache.conv.get((i, "in"), self.x), s.qo_indptr, s.row_req, s.pos,
+                               s.slots, s.B, out=h, residual=True)
+            else:
+                ops.cast_rows(x, h)
+            if L.kind == "latent":
+                m = L.mixer
+                nq = m.heads * (m.dim + m.rot_dim)
+                nc = m.kv_rank + m.rot_dim if m.kv_from is None else 0
+                P = nq + nc + (m.heads * m.vdim if m.value_gate else 0)
+                proj = self._proj(h, lw["in"], self.proj[:T * P].view(T, P))
+                y = self._latent_direct(i, m, lw, s, proj, gate=proj[:, nq + nc:] if m.value_gate else None)
+            else:
+                y = self._mixer_pair(i, L.mixer, lw, s)
+            ops.rms_postnorm_residual_f32(x, y, lw["norm1"], eps, out=h if L.mlp is not None else None)
+            if L.mlp is not None:
+                ops.rms_postnorm_residual_f32(x, self._moe(L.mlp, lw, s), lw["norm2"], eps)
+            if self.layer_tap is not None:
+                self.layer_tap.append(x.clone())
+        return self._head(s)
+
+    def _mixer_pair(self, i: int, m: MixerPairConfig, w: Dict[str, Any], s: StepInputs) -> torch.Tensor:
+        """Pooled-window sigmoid attention and a selective scan side by side on one fused input projection; both write their
+        (scaled) outputs next to each other, so ONE output projection over [W_o left | W_o right] sums them."""
+        T, a, r, cache, eps = s.T, m.left, m.right, self.cache, self.cfg.eps
+        H, G, D, V = a.heads, a.kv_heads, a.dim, a.vdim
+        nq, nk, nv, inner, N, dr = H * D, G * D, G * V, r.inner, r.state, r.dt_rank
+        nqkv = nq + nk + nv
+        P = nqkv + 2 * inner
+        proj = self._proj(self.h[:T], w["in"], self.proj[:T * P].view(T, P))
+        conv_args = (s.qo_indptr, s.row_req, s.pos, s.slots, s.B)
+        # ---- left: convolutions, whole-projection norms, append, pooled blocks, attention ----
+        qkv = proj[:, :nqkv]
+        if a.conv > 1:
+            qkv2 = self.proj2[:T * nqkv].view(T, nqkv)
+            ops.short_conv(qkv, w["qkv_conv"], None, cache.conv[(i, "qkv")], *conv_args, out_f32=qkv2)
+            qkv = qkv2
+        q = self.q[:T * nq].view(T, nq)
+        kc, vc = cache.k[i], cache.v[i]
+        ops.qk_norm_append(qkv, 0, nq, nq + nk, w.get("q_norm"), w.get("k_norm"), eps, q, kc, vc, s.row_req, s.pos, s.page_indptr,
+                           s.page_indices, T)
+        kp = vp = None
+        if a.pool > 0:
+            kp, vp = cache.k_pool[i], cache.v_pool[i]
+            ops.pool_blocks(kp, vp, kc, vc, a.pool, s.qo_indptr, s.pos, s.page_indptr, s.page_indices, T, s.B)
+        mix = self.mix_out[:T * (H * V + inner)].view(T, H * V + inner)
+        args = (q, kc, vc, kp, vp, w["head_bias"], mix[:, :H * V], s.row_req, s.pos, s.page_indptr, s.page_indices, T, H, a.window,
+                a.pool, a.scale, a.softcap, m.left_scale)
+        capacity = cache.num_pages * cache.page_size
+        keys = dict(scratch=self.attn_part, max_keys=(min(a.window, capacity) + capacity // max(a.pool, 1)) if a.window > 0 else capacity)
+        if s.tiles is not None and self.use_tiled_attention and (not s.single or s.single_rows is not None):
+            ops.sigmoid_attn(*args, tiles=(s.qo_indptr, s.tiles[0], s.tiles[1], s.tiles[2], self.lin_tile_rows))
+            if s.single:
+                ops.sigmoid_attn(*args, rows=s.single_rows, **keys)
+        else:
+            ops.sigmoid_attn(*args, **keys)
+        # ---- right: convolution + silu, low-rank projection, step sizes, scan ----
+        xc32, xc = self.scan_x[:T * inner].view(T, inner), self.scan_xc[:T * inner].view(T, inner)
+        ops.short_conv(proj[:, nqkv:nqkv + inner], w["x_conv"], w["x_conv_b"], cache.conv[(i, "x")], *conv_args, out=xc, out_f32=xc32,
+                       act="silu")
+        low = self._proj(xc, w["x_proj"], self.scan_low[:T * (dr + 2 * N)].view(T, dr + 2 * N))
+        dtl = ops.cast_rows(low[:, :dr], self.scan_dtl[:T * dr].view(T, dr))
+        dt = self._proj(dtl, w["dt_proj"], self.scan_dt[:T * inner].view(T, inner))
+        z = proj[:, nqkv + inner:]
+        scan = (xc32, dt, w["dt_b"], low, dr, dr + N, z, w["A"], w["D"], cache.state[i], mix[:, H * V:], s.qo_indptr, s.pos, s.slots, s.B)
+        par = (s.multi and s.tiles is not None and self.use_tiled_recurrence and self.scan_scratch is not None and
+               ops.selective_scan_scratch_floats(s.tiles[2], self.lin_tile_rows, inner, N) <= self.scan_scratch.numel())
+        if s.single or (s.multi and not par):
+            ops.selective_scan(*scan, out_scale=m.right_scale, single_rows=s.single, multi_rows=s.multi and not par)
+        if par:
+            ops.selective_scan(*scan, out_scale=m.right_scale, tiles=(s.tiles[0], s.tiles[1], s.tiles[2], self.lin_tile_rows),
+                               scratch=self.scan_scratch)
+        return self._proj(mix, w["o"], self.y[:T])

@@ -1,7 +1,7 @@
 """Model-adapter registry with the reference's public surface (``vox_serve/model/__init__.py:17-179``):
 ``MODEL_REGISTRY``, ``get_model_class``, ``load_model``, ``register_model``, ``list_supported_models``.
 Only adapters whose whole decode + vocoder path runs on the sm_100a kernels are registered: Orpheus (+ SNAC) and CSM
-(+ Mimi) and Qwen3-TTS (+ its streaming 12 Hz codec decoder), and the text-only Bobavik, Razevik and Fovunex LMs.  A model given as a local
+(+ Mimi) and Qwen3-TTS (+ its streaming 12 Hz codec decoder), and the text-only Bobavik, Razevik, Fovunex and Nadevik LMs.  A model given as a local
 directory is matched by the ``architecture`` of its ``config.json`` first, by its name otherwise."""
 from __future__ import annotations
 
@@ -16,6 +16,7 @@ from .base import BaseLM, BaseLMWithDepth, PreprocessOutput
 from .bobavik import BobavikModel
 from .csm import CSMModel
 from .fovunex import FovunexModel
+from .nadevik import NadevikModel
 from .orpheus import OrpheusModel
 from .qwen3_tts import Qwen3TTSModel
 from .razevik import RazevikModel
@@ -30,6 +31,7 @@ MODEL_REGISTRY: Dict[str, Type[BaseLM]] = {
     "bobavik": BobavikModel,
     "razevik": RazevikModel,
     "fovunex": FovunexModel,
+    "nadevik": NadevikModel,
 }
 
 

@@ -1148,13 +1148,16 @@ def latent_rope_append(proj: torch.Tensor, q_off: int, c_off: int, H: int, dim: 
     shared rotated key part (rot) at c_off.  The latent is RMS-normed (wc) and appended with the rotated key part to cache
     [pages, page, 1, kv_rank + rot]; the queries' unrotated parts go to q_out [T, H, dim], their rotated parts to
     q_lat[:, :, kv_rank:] (q_lat [T, H, kv_rank + rot])."""
-    _need_cuda(proj, q_out, q_lat, cache)
-    assert proj.dtype == F32 and proj.stride(1) == 1 and wc.dtype == F32 and wc.numel() == kv_rank
-    assert cache.dtype == q_out.dtype == q_lat.dtype and cache.is_contiguous() and q_out.is_contiguous() and q_lat.is_contiguous()
-    assert cache.shape[-1] == kv_rank + rot and q_lat.shape[-1] == kv_rank + rot
-    call("vb_latent_rope_append", proj.data_ptr(), proj.stride(0), q_off, c_off, H, dim, rot, kv_rank, wc.data_ptr(), _p(cs),
-         half, ROTARY_LAYOUTS[layout], q_out.data_ptr(), q_lat.data_ptr(), cache.data_ptr(), row_req.data_ptr(), pos.data_ptr(),
-         page_indptr.data_ptr(), page_indices.data_ptr(), cache.shape[1], T, float(eps), _dt(q_out), _stream())
+    _need_cuda(proj, q_out, q_lat)
+    assert proj.dtype == F32 and proj.stride(1) == 1 and q_out.dtype == q_lat.dtype
+    assert q_out.is_contiguous() and q_lat.is_contiguous() and q_lat.shape[-1] == kv_rank + rot
+    if cache is not None:      # (None: the layer attends over rows another layer cached; only its queries are laid out)
+        assert wc.dtype == F32 and wc.numel() == kv_rank
+        assert cache.dtype == q_out.dtype and cache.is_contiguous() and cache.shape[-1] == kv_rank + rot
+    call("vb_latent_rope_append", proj.data_ptr(), proj.stride(0), q_off, c_off, H, dim, rot, kv_rank, _p(wc), _p(cs),
+         half, ROTARY_LAYOUTS[layout], q_out.data_ptr(), q_lat.data_ptr(), _p(cache), row_req.data_ptr(), pos.data_ptr(),
+         page_indptr.data_ptr(), page_indices.data_ptr(), cache.shape[1] if cache is not None else 1, T, float(eps), _dt(q_out),
+         _stream())
 
 
 def head_pair_combine(a: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor], H: int, R: int, vdim: int, lam: float,
@@ -1368,3 +1371,202 @@ def moe_scale_dense(act: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, exp
     call("vb_moe_scale_dense", act.data_ptr(), idx.data_ptr(), wts.data_ptr(), act.shape[0], act.stride(0), experts, ff, top,
          _p(shared_gate), int(shared_ff), _stream())
     return act
+
+
+# ----------------------------------------------------------------------------------------------
+# post-norm stacks with short convolutions, pooled-window sigmoid attention, a selective scan (norm_linear.cu, short_conv.cu,
+# sigmoid_attn.cu, selective_scan.cu)
+# ----------------------------------------------------------------------------------------------
+def rms_postnorm_residual_f32(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float,
+                              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x += y / sqrt(mean(y^2) + eps) * w in place (fp32 [T, W]); out (bf16 or fp32, optional) = the new x."""
+    _need_cuda(x, y, w)
+    assert x.dtype == F32 and y.dtype == F32 and w.dtype == F32 and x.is_contiguous() and y.is_contiguous()
+    assert tuple(x.shape) == tuple(y.shape) and w.numel() == x.shape[1] and (out is None or out.is_contiguous())
+    call("vb_rms_postnorm_residual_f32", x.data_ptr(), y.data_ptr(), w.data_ptr(), _p(out), x.shape[0], x.shape[1], float(eps),
+         _dt(out) if out is not None else 1, _stream())
+    return x
+
+
+def linear_batched_gated(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """``linear_batched`` whose gate holds one value per OUTPUT value: out[t, g, n] *= sigmoid(gate[t, g * N + n]); gate an fp32
+    view [T, >= G * N] with any row stride."""
+    _need_cuda(x, w, out, gate)
+    T, G, K = x.shape
+    N = w.shape[1]
+    assert x.dtype == w.dtype and x.stride(2) == 1 and w.is_contiguous() and out.stride(2) == 1
+    assert tuple(w.shape) == (G, N, K) and tuple(out.shape) == (T, G, N)
+    assert gate.dtype == F32 and gate.stride(1) == 1 and gate.shape[1] >= G * N
+    call("vb_linear_batched_gated", out.data_ptr(), x.data_ptr(), w.data_ptr(), T, N, K, x.stride(0), out.stride(0), x.stride(1),
+         out.stride(1), N * K, G, _dt(x), _dt(out), 0, 1.0, gate.data_ptr(), gate.stride(0), 1, _stream())
+    return out
+
+
+def pair_hash_rows(rows: torch.Tensor, prev_tok: torch.Tensor, ids: torch.Tensor, qo_indptr: torch.Tensor,
+                   row_req: torch.Tensor, pos: torch.Tensor, slots: torch.Tensor, T: int, buckets: int, mul_prev: int,
+                   mul_cur: int) -> torch.Tensor:
+    """rows[t] = (previous token * mul_prev + ids[t] * mul_cur) mod buckets, ``buckets`` for a request's first token; the token
+    before a step's first row is prev_tok[slot] (int32 [slots]), which then takes the step's last token."""
+    _need_cuda(rows, prev_tok, ids)
+    assert rows.dtype == prev_tok.dtype == ids.dtype == torch.int32
+    call("vb_pair_hash_rows", rows.data_ptr(), prev_tok.data_ptr(), ids.data_ptr(), qo_indptr.data_ptr(), row_req.data_ptr(),
+         pos.data_ptr(), slots.data_ptr(), T, int(buckets), int(mul_prev), int(mul_cur), _stream())
+    return rows
+
+
+def short_conv(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor, qo_indptr: torch.Tensor,
+               row_req: torch.Tensor, pos: torch.Tensor, slots: torch.Tensor, B: int, out: Optional[torch.Tensor] = None,
+               out_f32: Optional[torch.Tensor] = None, act: Optional[str] = None, residual: bool = False) -> None:
+    """Causal convolution over time on every channel of x (an fp32 view [T, C], any row stride): y_t = bias + sum_j w[:, j]
+    x_(t - taps + 1 + j), zeros before a request's start; w fp32 [C, taps]; act "silu" or None; residual: x_t is added to the
+    result.  state fp32 [slots, taps - 1, C]: a request's last inputs, read by the step's first rows and advanced by the step.
+    out (bf16 or fp32 view [T, C]) and / or out_f32 (fp32 view) receive the result."""
+    _need_cuda(x, w, state)
+    T, C = x.shape
+    taps = w.shape[1]
+    assert x.dtype == F32 and x.stride(1) == 1 and w.dtype == F32 and w.is_contiguous() and w.shape[0] == C
+    assert state.dtype == F32 and state.is_contiguous() and (taps == 1 or tuple(state.shape[1:]) == (taps - 1, C))
+    assert bias is None or (bias.dtype == F32 and bias.numel() == C)
+    for o in (out, out_f32):
+        assert o is None or (o.stride(1) == 1 and tuple(o.shape) == (T, C))
+    assert out_f32 is None or out_f32.dtype == F32
+    call("vb_short_conv", _p(out), out.stride(0) if out is not None else 0, _p(out_f32),
+         out_f32.stride(0) if out_f32 is not None else 0, x.data_ptr(), x.stride(0), w.data_ptr(), _p(bias), state.data_ptr(),
+         qo_indptr.data_ptr(), row_req.data_ptr(), pos.data_ptr(), slots.data_ptr(), T, B, C, taps, 1 if act == "silu" else 0,
+         int(residual), _dt(out) if out is not None else 1, _stream())
+
+
+def cast_rows(src: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out [T, n] (dense; bf16 or fp32) = src, an fp32 view [T, n] with any row stride."""
+    _need_cuda(src, out)
+    assert src.dtype == F32 and src.stride(1) == 1 and out.is_contiguous() and tuple(src.shape) == tuple(out.shape)
+    call("vb_cast_rows", out.data_ptr(), src.data_ptr(), src.stride(0), src.shape[0], src.shape[1], _dt(out), _stream())
+    return out
+
+
+def qk_norm_append(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_norm: Optional[torch.Tensor],
+                   k_norm: Optional[torch.Tensor], eps: float, q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                   row_req: torch.Tensor, pos: torch.Tensor, page_indptr: torch.Tensor, page_indices: torch.Tensor, T: int) -> None:
+    """proj fp32 [T, ld]: the queries (q_out.shape[1] columns at q_off) and the keys are RMS-normed over their WHOLE width
+    (weights fp32, one per column; None: no norm); queries to q_out [T, nq], keys and values appended to k_cache
+    [pages, page, G, dim] / v_cache [pages, page, G, vdim]."""
+    _need_cuda(proj, q_out, k_cache, v_cache)
+    assert proj.dtype == F32 and proj.stride(1) == 1 and k_cache.dtype == q_out.dtype == v_cache.dtype
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and q_out.is_contiguous()
+    nq, nk, nv = q_out.shape[1], k_cache.shape[2] * k_cache.shape[3], v_cache.shape[2] * v_cache.shape[3]
+    assert q_norm is None or (q_norm.dtype == F32 and q_norm.numel() == nq)
+    assert k_norm is None or (k_norm.dtype == F32 and k_norm.numel() == nk)
+    call("vb_qk_norm_append", proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, _p(q_norm), _p(k_norm), float(eps),
+         q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), row_req.data_ptr(), pos.data_ptr(), page_indptr.data_ptr(),
+         page_indices.data_ptr(), k_cache.shape[1], T, nq, nk, nv, _dt(q_out), _stream())
+
+
+def pool_blocks(k_pool: torch.Tensor, v_pool: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pool: int,
+                qo_indptr: torch.Tensor, pos: torch.Tensor, page_indptr: torch.Tensor, page_indices: torch.Tensor, T: int,
+                B: int) -> None:
+    """The blocks of ``pool`` positions that the step's rows complete: mean of their cached keys / values into k_pool / v_pool
+    (fp32 [pages, ceil(page / pool), G, dim / vdim])."""
+    _need_cuda(k_pool, v_pool, k_cache, v_cache)
+    page = k_cache.shape[1]
+    nk, nv = k_cache.shape[2] * k_cache.shape[3], v_cache.shape[2] * v_cache.shape[3]
+    assert k_pool.dtype == F32 and v_pool.dtype == F32 and k_pool.is_contiguous() and v_pool.is_contiguous()
+    assert k_pool.shape[1] == (page + pool - 1) // pool and k_pool.shape[0] == k_cache.shape[0]
+    call("vb_pool_blocks", k_pool.data_ptr(), v_pool.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), qo_indptr.data_ptr(),
+         pos.data_ptr(), page_indptr.data_ptr(), page_indices.data_ptr(), page, int(pool), T, B, nk, nv, _dt(k_cache), _stream())
+
+
+def sigmoid_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, k_pool: Optional[torch.Tensor],
+                 v_pool: Optional[torch.Tensor], head_bias: Optional[torch.Tensor], out: torch.Tensor, row_req: torch.Tensor,
+                 pos: torch.Tensor, page_indptr: torch.Tensor, page_indices: torch.Tensor, T: int, H: int, window: int, pool: int,
+                 scale: float, cap: float = 0.0, out_scale: float = 1.0,
+                 tiles: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor, int, int]] = None,
+                 rows: Optional[Tuple[torch.Tensor, int]] = None, scratch: Optional[torch.Tensor] = None,
+                 max_keys: int = 0) -> torch.Tensor:
+    """out[t, h * vdim : (h + 1) * vdim] = out_scale * sum_j sigmoid(cap * tanh(q . k_j * scale / cap) + head_bias[h]) v_j over
+    the tokens of the window and the pooled blocks wholly before it (no normalisation over the keys).  q [T, H * dim], caches
+    [pages, page, G, dim / vdim] (bf16 or fp32, as q and out); out a view [T, >= H * vdim] with any row stride.  tiles =
+    (qo_indptr, tile_req, tile_row0, n_tiles, tile_rows): the rows of those tiles; else the rows listed in ``rows`` (or all T).
+    scratch (fp32) + max_keys: lets a small step deal a row's keys to several CTAs."""
+    _need_cuda(q, k_cache, v_cache, out)
+    G, dim, vdim = k_cache.shape[2], k_cache.shape[3], v_cache.shape[3]
+    assert q.dtype == k_cache.dtype == v_cache.dtype == out.dtype and q.is_contiguous() and out.stride(1) == 1
+    assert pool <= 0 or (k_pool is not None and k_pool.dtype == F32 and v_pool.dtype == F32)
+    if tiles is not None:
+        qo, tile_req, tile_row0, n_tiles, tile_rows = tiles
+        tr, t0, rl, n_rows, qop = tile_req.data_ptr(), tile_row0.data_ptr(), None, 0, qo.data_ptr()
+    else:
+        tr = t0 = qop = None
+        n_tiles = tile_rows = 0
+        rl, n_rows = (rows[0].data_ptr(), rows[1]) if rows is not None else (None, T)
+    call("vb_sigmoid_attn", out.data_ptr(), out.stride(0), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _p(k_pool),
+         _p(v_pool), _p(head_bias), row_req.data_ptr(), pos.data_ptr(), page_indptr.data_ptr(), page_indices.data_ptr(), qop, tr,
+         t0, n_tiles, tile_rows, rl, n_rows, H, G, dim, vdim, k_cache.shape[1], int(window), int(pool), float(scale), float(cap),
+         float(out_scale), _p(scratch), scratch.numel() if scratch is not None else 0, int(max_keys), _dt(q), _stream())
+    return out
+
+
+def selective_scan_piece_rows() -> int:
+    return _lib.load().vb_selective_scan_piece_rows()
+
+
+def selective_scan_scratch_floats(n_tiles: int, tile_rows: int, inner: int, states: int) -> int:
+    return _lib.load().vb_selective_scan_scratch_floats(int(n_tiles), int(tile_rows), int(inner), int(states))
+
+
+def selective_scan(x: torch.Tensor, dt: torch.Tensor, dt_bias: Optional[torch.Tensor], bc: torch.Tensor, b_off: int, c_off: int,
+                   z: torch.Tensor, A: torch.Tensor, D: Optional[torch.Tensor], state: torch.Tensor, out: torch.Tensor,
+                   qo_indptr: torch.Tensor, pos: torch.Tensor, slots: torch.Tensor, B: int, out_scale: float = 1.0,
+                   single_rows: bool = True, multi_rows: bool = True,
+                   tiles: Optional[Tuple[torch.Tensor, torch.Tensor, int, int]] = None,
+                   scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """S[c, n] = exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n;  y_c = sum_n S[c, n] C_n + D_c x_c;  out = out_scale * y * silu(z) with
+    dt = softplus(dt + dt_bias).  x, dt, z: fp32 views [T, inner]; bc fp32 view [T, ld] with B at column b_off, C at c_off;
+    A fp32 [inner, N]; state fp32 [slots, inner, N] (taken as zero where a request starts at position 0); out a view
+    [T, inner] (bf16 or fp32).  tiles = (tile_req, tile_row0, n_tiles, tile_rows) + scratch: prompt portions in parallel pieces
+    (requests that bring one row are then left to a second call)."""
+    _need_cuda(x, dt, bc, z, A, state, out)
+    inner, N = A.shape
+    for t in (x, dt, z):
+        assert t.dtype == F32 and t.stride(1) == 1 and t.shape[1] == inner
+    assert bc.dtype == F32 and bc.stride(1) == 1 and A.dtype == F32 and A.is_contiguous() and state.dtype == F32
+    assert state.is_contiguous() and tuple(state.shape[1:]) == (inner, N) and out.stride(1) == 1 and out.shape[1] == inner
+    assert dt_bias is None or (dt_bias.dtype == F32 and dt_bias.numel() == inner)
+    assert D is None or (D.dtype == F32 and D.numel() == inner)
+    if tiles is None:
+        call("vb_selective_scan", out.data_ptr(), out.stride(0), state.data_ptr(), x.data_ptr(), x.stride(0), dt.data_ptr(),
+             dt.stride(0), _p(dt_bias), bc.data_ptr(), bc.stride(0), b_off, c_off, z.data_ptr(), z.stride(0), A.data_ptr(), _p(D),
+             qo_indptr.data_ptr(), pos.data_ptr(), slots.data_ptr(), B, inner, N, float(out_scale), int(single_rows),
+             int(multi_rows), _dt(out), _stream())
+    else:
+        tile_req, tile_row0, n_tiles, tile_rows = tiles
+        assert scratch is not None and scratch.dtype == F32
+        assert scratch.numel() >= selective_scan_scratch_floats(n_tiles, tile_rows, inner, N)
+        call("vb_selective_scan_tiled", out.data_ptr(), out.stride(0), state.data_ptr(), scratch.data_ptr(), x.data_ptr(),
+             x.stride(0), dt.data_ptr(), dt.stride(0), _p(dt_bias), bc.data_ptr(), bc.stride(0), b_off, c_off, z.data_ptr(),
+             z.stride(0), A.data_ptr(), _p(D), qo_indptr.data_ptr(), pos.data_ptr(), slots.data_ptr(), tile_req.data_ptr(),
+             tile_row0.data_ptr(), n_tiles, tile_rows, B, inner, N, float(out_scale), _dt(out), _stream())
+    return out
+
+
+def moe_route_groups(h: torch.Tensor, router_w: torch.Tensor, top: int, idx: torch.Tensor, wts: torch.Tensor, groups: int = 0,
+                     keep: int = 0, scores: str = "softmax", group_rank: str = "max", normalize: bool = False,
+                     correction: Optional[torch.Tensor] = None) -> None:
+    """Scores s = softmax(router_w h) over all experts ("softmax") or sigmoid(router_w h) ("sigmoid"), fp32; the ``top`` largest
+    s (+ correction) among the experts of the ``keep`` best of ``groups`` groups of neighbours, a group ranked by its largest
+    ("max") or its two largest ("top2") corrected scores; weights = the chosen s, divided by their sum if ``normalize``."""
+    _need_cuda(h, router_w, idx, wts)
+    assert router_w.dtype == F32 and idx.dtype == torch.int32 and wts.dtype == F32 and h.is_contiguous()
+    call("vb_moe_route_groups", idx.data_ptr(), wts.data_ptr(), None, h.data_ptr(), router_w.data_ptr(), _p(correction), None,
+         h.shape[0], h.shape[1], router_w.shape[0], top, int(groups), int(keep), int(scores == "softmax"),
+         int(group_rank == "max"), int(normalize), _dt(h), _stream())
+
+
+def gemm_grouped_glu(x: torch.Tensor, w: "PackedWeight", out: torch.Tensor, N: int, K: int, t_tile: int,
+                     tile_group: torch.Tensor, group_bytes: int, limit: float, slope: float) -> torch.Tensor:
+    """``gemm_grouped`` with the clamped gated epilogue of ``gemm_glu``: row tiles times their group's interleaved gate / up rows
+    (N = 2 * ff rows per group), out bf16 [rows, N / 2]."""
+    _need_cuda(x, out)
+    assert x.dtype == BF16 and x.dim() == 2 and x.shape[1] == K and out.is_contiguous() and x.shape[0] % t_tile == 0
+    call("vb_gemm_bf16_grouped_glu", out.data_ptr(), w.data.data_ptr(), tensor_map_2d(x, t_tile).ptr, x.shape[0], N, K, N // 2,
+         w.tile_rows, N // 2, t_tile, _p(tile_group), int(group_bytes), float(limit), float(slope), _stream())
+    return out
