@@ -623,12 +623,12 @@ def main():
     ap.add_argument("--ttfa-joins", type=int, default=20, help="joins measured for ttfa_join_ms (0 = skip)")
     ap.add_argument("--profile-steps", type=int, default=0,
                     help="after the timed regions run this many resident steps inside cudaProfilerStart/Stop (ncu)")
-    ap.add_argument("--arch", default=None, choices=["bobavik", "razevik", "fovunex"],
+    ap.add_argument("--arch", default=None, choices=["bobavik", "razevik", "fovunex", "nadevik"],
                     help="instead of the headline workload: prefill / decode throughput of that design beside its closest "
                          "relative at equal size (bobavik: the Llama-shaped engine; razevik: Bobavik with attention layers "
-                         "only; fovunex: Bobavik; benchmarks/hybrid_bench.py); one JSON line per size")
+                         "only; fovunex, nadevik: Bobavik; benchmarks/hybrid_bench.py); one JSON line per size")
     ap.add_argument("--arch-sizes", default="2048,3072", help="model widths of the --arch comparison")
-    ap.add_argument("--arch-only", default="", choices=["", "bobavik", "llama", "razevik", "fovunex"], help="run one side of the comparison")
+    ap.add_argument("--arch-only", default="", choices=["", "bobavik", "llama", "razevik", "fovunex", "nadevik"], help="run one side of the comparison")
     args = ap.parse_args()
     if args.arch is not None:
         from benchmarks import hybrid_bench

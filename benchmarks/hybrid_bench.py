@@ -12,6 +12,11 @@ expert sizes.
 two score maps per head in chunks, minGRU, clamped gated dense feed-forward) beside Bobavik (softmax attention and linear
 attention with a recurrent state, mixture of experts) at equal width, head count and feed-forward width per token.
 
+``--arch nadevik``: the Nadevik design (post-norm blocks with an input convolution; windowed latent attention with a shared
+rotated key part, own and shared cached rows; pooled-window sigmoid attention beside a selective scan; group-limited softmax
+router over clamped gated experts; tied head) beside Bobavik (window attention, linear attention with a recurrent state,
+mixture of experts) at equal width, head count, head size and expert width per token.
+
 Per size and engine: prefill of one 1024-token prompt (eager launches) and one decode step of 32 requests at context 512
 (a CUDA-graph replay, as served), timed with CUDA events after warm-up; an L2-sized buffer is overwritten between timed
 iterations.  Output: one JSON line per size.
@@ -61,6 +66,28 @@ def fovunex_config(width: int, ff: int) -> dict:
             "layers": layers}
 
 
+def nadevik_config(width: int, ff: int, experts: int = 8, top: int = 3) -> dict:
+    """four layers: latent attention (own cached rows), two mixer pairs, latent attention reading the first layer's rows; every
+    layer with experts.  128-wide heads (latent attention: 128 unrotated + 64 rotated dims on a latent of 128, window 4096;
+    sigmoid attention: a quarter as many key/value heads, window 512 with pooled blocks of 16, convolutions of 3 taps; scan:
+    twice the width, 16 states, step sizes of rank width / 16, convolution of 4 taps); 8 experts in 4 groups (keep 3), top 3 --
+    the expert width a Bobavik token uses (top 2 + shared)"""
+    heads = width // 128
+    lat = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 128, "scale": 192 ** -0.5, "mask": {"size": 4096},
+           "rot": {"base": 1e4, "dims": 64}}
+    left = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
+            "conv": 3, "mask": {"size": 512, "pool": 16}}
+    right = {"inner": 2 * width, "state": 16, "dt_rank": width // 16, "conv": 4}
+    pair = {"left": left, "right": right, "left_scale": 0.7, "right_scale": 0.7}
+    mlp = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": experts, "top": top, "groups": {"count": 4, "keep": 3}}}
+    layers = [{"type": "latent_attention", "mixer": dict(lat), "mlp": dict(mlp)},
+              {"type": "parallel", "mixer": dict(pair), "mlp": dict(mlp)},
+              {"type": "parallel", "mixer": dict(pair), "mlp": dict(mlp)},
+              {"type": "latent_attention", "mixer": dict(lat, kv_from=0), "mlp": dict(mlp)}]
+    return {"architecture": "Nadevik", "width": width, "vocab": VOCAB, "norm": {"eps": 1e-6}, "canon": {"taps": 4},
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 8191, "mul_prev": 31, "mul_cur": 7}}, "layers": layers}
+
+
 def bobavik_config(width: int, ff: int, experts: int = 8, top: int = 2, window: int = 4096,
                    kinds=("attention", "lightning", "lightning", "attention")) -> dict:
     heads = width // 128
@@ -108,9 +135,12 @@ def bench_bobavik(width: int, ff: int, steps: int, warmup: int, flush, kinds=Non
     from vox_serve_b200.hybrid_engine import StepInputs
     from vox_serve_b200.model.bobavik import BobavikModel
     from vox_serve_b200.model.fovunex import FovunexModel
+    from vox_serve_b200.model.nadevik import NadevikModel
     from vox_serve_b200.model.razevik import RazevikModel
 
-    if design == "fovunex":
+    if design == "nadevik":
+        model = NadevikModel("nadevik-synthetic:1", config=nadevik_config(width, ff), device="cuda:0")
+    elif design == "fovunex":
         model = FovunexModel("fovunex-synthetic:1", config=fovunex_config(width, ff), device="cuda:0")
     elif design == "razevik":
         model = RazevikModel("razevik-synthetic:1", config=razevik_config(width, ff), device="cuda:0")
@@ -209,6 +239,17 @@ def run(sizes, steps: int, warmup: int, only: str = "", arch: str = "bobavik") -
                     "l2": "192 MiB buffer overwritten between timed iterations"}
             if only in ("", "fovunex"):
                 line["fovunex"] = bench_bobavik(width, ff, steps, warmup, flush, design="fovunex")
+            if only in ("", "bobavik"):
+                line["bobavik"] = bench_bobavik(width, ff, steps, warmup, flush)
+            print(json.dumps(line), flush=True)
+            torch.cuda.empty_cache()
+            continue
+        if arch == "nadevik":
+            line = {"bench": "nadevik_vs_bobavik", "width": width, "layers": LAYERS, "prompt": PROMPT, "decode_batch": BATCH,
+                    "context": CONTEXT, "steps": steps, "warmup": warmup, "dtype": "bf16", "data": "synthetic",
+                    "l2": "192 MiB buffer overwritten between timed iterations"}
+            if only in ("", "nadevik"):
+                line["nadevik"] = bench_bobavik(width, ff, steps, warmup, flush, design="nadevik")
             if only in ("", "bobavik"):
                 line["bobavik"] = bench_bobavik(width, ff, steps, warmup, flush)
             print(json.dumps(line), flush=True)

@@ -108,22 +108,12 @@ def pooled_blocks(i: int, size: int, pool: int) -> List[int]:
 
 
 # ---- mixers ----------------------------------------------------------------------------------------------------------
-def pooled_sigmoid_attention(m: Dict[str, Any], sd, p: str, h: torch.Tensor, eps: float) -> torch.Tensor:
-    """Grouped-head attention without rotation and without softmax: short causal convolutions on q, k, v; RMS norm of q and
-    of k over their whole projection; soft-capped scores; keys = the window's tokens plus the means of the blocks wholly
-    before it; weight sigmoid(score + bias of the head), not normalised."""
-    T = h.shape[0]
-    H, G, D, V = int(m["heads"]), int(m.get("kv_heads", m["heads"])), int(m["dim"]), int(m.get("vdim", m["dim"]))
-    q, k, v = h @ _w(sd, p + "q").T, h @ _w(sd, p + "k").T, h @ _w(sd, p + "v").T
-    if int(m.get("conv", 0) or 0):
-        q, k, v = (causal_conv(t, _w(sd, p + n + ".conv")) for t, n in ((q, "q"), (k, "k"), (v, "v")))
-    q = unit_rms(q, eps) * _w(sd, p + "q.norm")
-    k = unit_rms(k, eps) * _w(sd, p + "k.norm")
-    q, k, v = q.view(T, H, D), k.view(T, G, D), v.view(T, G, V)
-    mask = m.get("mask") or {}
-    size, pool = int(mask.get("size", 0) or 0), int(mask.get("pool", 0) or 0)
-    cap = float(m.get("softcap", 0.0) or 0.0)
-    pb = _w(sd, p + "pb")
+def sigmoid_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, bias: torch.Tensor, scale: float, cap: float,
+                   size: int, pool: int) -> torch.Tensor:
+    """q [T, H, D], k [T, G, D], v [T, G, V] of ONE sequence from position 0 -> [T, H, V]: position i weighs the tokens of its
+    window and the means of the blocks wholly before it by sigmoid(capped score + bias[head]); nothing is normalised."""
+    T, H, _ = q.shape
+    G, V = k.shape[1], v.shape[2]
     out = torch.zeros(T, H, V, dtype=F64)
     for i in range(T):
         js, bs = window_keys(i, size), pooled_blocks(i, size, pool)
@@ -131,11 +121,40 @@ def pooled_sigmoid_attention(m: Dict[str, Any], sd, p: str, h: torch.Tensor, eps
             g = hh // (H // G)
             keys = [k[b * pool:(b + 1) * pool, g].mean(0) for b in bs] + [k[j, g] for j in js]
             vals = [v[b * pool:(b + 1) * pool, g].mean(0) for b in bs] + [v[j, g] for j in js]
-            s = torch.stack(keys) @ q[i, hh] * float(m["scale"])
+            s = torch.stack(keys) @ q[i, hh] * scale
             if cap:
                 s = cap * torch.tanh(s / cap)
-            out[i, hh] = sigmoid(s + pb[hh]) @ torch.stack(vals)
+            out[i, hh] = sigmoid(s + bias[hh]) @ torch.stack(vals)
+    return out
+
+
+def pooled_sigmoid_attention(m: Dict[str, Any], sd, p: str, h: torch.Tensor, eps: float) -> torch.Tensor:
+    """Grouped-head attention without rotation and without softmax: short causal convolutions on q, k, v; RMS norm of q and
+    of k over their whole projection; soft-capped scores; keys = the window's tokens plus the means of the blocks wholly
+    before it; weight sigmoid(score + bias of the head), not normalised."""
+    T = h.shape[0]
+    H, G, D, V = int(m["heads"]), int(m.get("kv_heads", m["heads"])), int(m["dim"]), int(m.get("vdim", m["dim"]))
+    q, k, v = h @ _w(sd, p + "q").T, h @ _w(sd, p + "k").T, h @ _w(sd, p + "v").T
+    if int(m.get("conv", 0) or 0) >= 1:
+        q, k, v = (causal_conv(t, _w(sd, p + n + ".conv")) for t, n in ((q, "q"), (k, "k"), (v, "v")))
+    q = unit_rms(q, eps) * _w(sd, p + "q.norm")
+    k = unit_rms(k, eps) * _w(sd, p + "k.norm")
+    mask = m.get("mask") or {}
+    out = sigmoid_attend(q.view(T, H, D), k.view(T, G, D), v.view(T, G, V), _w(sd, p + "pb"), float(m["scale"]),
+                         float(m.get("softcap", 0.0) or 0.0), int(mask.get("size", 0) or 0), int(mask.get("pool", 0) or 0))
     return out.reshape(T, H * V) @ _w(sd, p + "o").T
+
+
+def scan(x: torch.Tensor, dt: torch.Tensor, Bm: torch.Tensor, Cm: torch.Tensor, A: torch.Tensor, Dv: torch.Tensor,
+         S: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """x, dt [T, inner]; Bm, Cm [T, N]; A [inner, N]; S the state before the first row (None: zero) -> (y [T, inner], S after)."""
+    T, inner = x.shape
+    S = torch.zeros(inner, A.shape[1], dtype=F64) if S is None else S.clone()
+    y = torch.zeros(T, inner, dtype=F64)
+    for t in range(T):
+        S = torch.exp(dt[t, :, None] * A) * S + (dt[t] * x[t])[:, None] * Bm[t][None, :]
+        y[t] = S @ Cm[t] + Dv * x[t]
+    return y, S
 
 
 def selective_scan(m: Dict[str, Any], sd, p: str, h: torch.Tensor) -> torch.Tensor:
@@ -147,14 +166,7 @@ def selective_scan(m: Dict[str, Any], sd, p: str, h: torch.Tensor) -> torch.Tens
     x = silu(causal_conv(x, _w(sd, p + "conv"), _w(sd, p + "conv.b")))
     low = x @ _w(sd, p + "x").T
     dt = softplus(low[:, :R] @ _w(sd, p + "dt").T + _w(sd, p + "dt.b"))
-    Bm, Cm = low[:, R:R + N], low[:, R + N:R + 2 * N]
-    A = -torch.exp(_w(sd, p + "A_log"))
-    Dv = _w(sd, p + "D")
-    S = torch.zeros(inner, N, dtype=F64)
-    y = torch.zeros(T, inner, dtype=F64)
-    for t in range(T):
-        S = torch.exp(dt[t, :, None] * A) * S + (dt[t] * x[t])[:, None] * Bm[t][None, :]
-        y[t] = S @ Cm[t] + Dv * x[t]
+    y, _ = scan(x, dt, low[:, R:R + N], low[:, R + N:R + 2 * N], -torch.exp(_w(sd, p + "A_log")), _w(sd, p + "D"))
     return (y * silu(z)) @ _w(sd, p + "o").T
 
 
@@ -260,3 +272,103 @@ def forward(cfg: Dict[str, Any], sd: Dict[str, torch.Tensor], tokens: List[int],
         if taps is not None:
             taps.append(x.clone())
     return one_plus_norm(x, _w(sd, "final.norm"), eps) @ _w(sd, "embed").T
+
+
+# ---- small configurations and random weights for the tests -----------------------------------------------------------
+def make_config(layers=("latent", "pair", "pair-", "shared:0", "pair"), width=48, vocab=97, eps=1e-5, embed_scale=3.0,
+                bigram=(53, 5, 3), canon=3, l_heads=3, l_dim=8, l_rot=6, l_rot_dims=None, l_vdim=10, l_rank=12, l_window=11,
+                l_base=300.0, a_heads=4, a_kv_heads=2, a_dim=12, a_vdim=6, a_window=9, a_pool=4, a_cap=5.0, a_conv=3,
+                s_inner=40, s_state=5, s_rank=6, s_conv=4, left_scale=0.7, right_scale=1.3, experts=6, top=2, ff=24, limit=1.2,
+                groups=(3, 2)) -> Dict[str, Any]:
+    """layers: "latent" (own cached rows), "shared:<j>" (reads layer j's), "pair"; a trailing "-" leaves the feed-forward out."""
+    out = []
+    for spec in layers:
+        has_ff = not spec.endswith("-")
+        kind = spec.rstrip("-")
+        if kind == "pair":
+            left = {"heads": a_heads, "kv_heads": a_kv_heads, "dim": a_dim, "vdim": a_vdim, "scale": 0.31, "softcap": a_cap,
+                    "conv": a_conv, "mask": {"size": a_window, "pool": a_pool}}
+            right = {"inner": s_inner, "state": s_state, "dt_rank": s_rank, "conv": s_conv}
+            layer = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": left_scale, "right_scale": right_scale}}
+        else:
+            m = {"heads": l_heads, "dim": l_dim, "rot_dim": l_rot, "vdim": l_vdim, "kv_rank": l_rank, "scale": 0.27,
+                 "mask": {"size": l_window}}
+            if l_rot:
+                m["rot"] = {"base": l_base, "dims": l_rot if l_rot_dims is None else l_rot_dims}
+            if kind.startswith("shared:"):
+                m["kv_from"] = int(kind.split(":")[1])
+            layer = {"type": "latent_attention", "mixer": m}
+        layer["mlp"] = None
+        if has_ff:
+            r = {"experts": experts, "top": top}
+            if groups:
+                r["groups"] = {"count": groups[0], "keep": groups[1]}
+            layer["mlp"] = {"kind": "moe", "expert": {"ff": ff, "limit": limit}, "router": r}
+        out.append(layer)
+    cfg = {"architecture": "Nadevik", "width": width, "vocab": vocab, "norm": {"eps": eps},
+           "embedding": {"scale": embed_scale}, "layers": out}
+    if canon:
+        cfg["canon"] = {"taps": canon}
+    if bigram:
+        cfg["embedding"]["bigram"] = {"buckets": bigram[0], "mul_prev": bigram[1], "mul_cur": bigram[2]}
+    return cfg
+
+
+def make_weights(cfg: Dict[str, Any], seed: int = 0, calm: bool = False) -> Dict[str, torch.Tensor]:
+    """Random bf16 weights with the checkpoint's names, scaled so that every mechanism matters in the logits.  calm: smaller
+    inputs and routers that are less sharp, for comparisons in bfloat16 (where a sharp router turns a rounding into another
+    expert)."""
+    g = torch.Generator().manual_seed(seed)
+    W = int(cfg["width"])
+    hot = 0.5 if calm else 1.0
+
+    def rnd(*shape, std=1.0, mean=0.0):
+        return (torch.randn(tuple(shape), generator=g) * std + mean).to(torch.bfloat16)
+
+    sd = {"embed": rnd(int(cfg["vocab"]), W, std=0.5 * hot), "final.norm": rnd(W, std=0.2)}
+    b = (cfg.get("embedding") or {}).get("bigram")
+    if b:
+        sd["bigram"] = rnd(int(b["buckets"]) + 1, W, std=hot)
+    taps = int((cfg.get("canon") or {}).get("taps", 0) or 0)
+    s = W ** -0.5
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        sd[p + "norm1"] = rnd(W, std=0.2)
+        if taps:
+            sd[p + "canon1"] = rnd(W, taps, std=0.4)
+        if L["type"] == "latent_attention":
+            H, D, Rd, V, R = (int(m[k]) for k in ("heads", "dim", "rot_dim", "vdim", "kv_rank"))
+            sd[p + "mix.q"] = rnd(H * (D + Rd), W, std=2 * s)
+            if m.get("kv_from") is None:
+                sd[p + "mix.dkv"], sd[p + "mix.dkv.norm"] = rnd(R + Rd, W, std=2 * s), rnd(R, std=0.2, mean=1.0)
+            sd[p + "mix.uk"], sd[p + "mix.uv"] = rnd(H * D, R, std=R ** -0.5), rnd(H * V, R, std=R ** -0.5)
+            sd[p + "mix.g"] = rnd(H * V, W, std=2 * s)
+            sd[p + "mix.o"] = rnd(W, H * V, std=(H * V) ** -0.5)
+        else:
+            a, r = m["left"], m["right"]
+            H, G, D, V = int(a["heads"]), int(a.get("kv_heads", a["heads"])), int(a["dim"]), int(a["vdim"])
+            lp, rp = p + "mix.left.", p + "mix.right."
+            sd[lp + "q"], sd[lp + "k"], sd[lp + "v"] = rnd(H * D, W, std=s), rnd(G * D, W, std=s), rnd(G * V, W, std=s)
+            sd[lp + "q.norm"], sd[lp + "k.norm"] = rnd(H * D, std=0.3, mean=1.5), rnd(G * D, std=0.3, mean=1.5)
+            if int(a.get("conv", 0) or 0) >= 1:
+                for n, c in (("q", H * D), ("k", G * D), ("v", G * V)):
+                    sd[lp + n + ".conv"] = rnd(c, int(a["conv"]), std=0.6)
+            sd[lp + "pb"] = rnd(H, std=0.7, mean=-1.0)
+            sd[lp + "o"] = rnd(W, H * V, std=(H * V) ** -0.5)
+            inner, N, R = int(r["inner"]), int(r["state"]), int(r["dt_rank"])
+            sd[rp + "in"] = rnd(2 * inner, W, std=s)
+            sd[rp + "conv"], sd[rp + "conv.b"] = rnd(inner, int(r["conv"]), std=0.6), rnd(inner, std=0.2)
+            sd[rp + "x"] = rnd(R + 2 * N, inner, std=2 * inner ** -0.5)
+            sd[rp + "dt"], sd[rp + "dt.b"] = rnd(inner, R, std=R ** -0.5), rnd(inner, std=0.7, mean=-1.5)
+            sd[rp + "A_log"] = torch.log(torch.rand(inner, N, generator=g) * 3.0 + 0.05).to(torch.bfloat16)
+            sd[rp + "D"] = rnd(inner, std=0.5)
+            sd[rp + "o"] = rnd(W, inner, std=inner ** -0.5)
+        f = L.get("mlp")
+        if f:
+            E, ff = int(f["router"]["experts"]), int(f["expert"]["ff"])
+            sd[p + "norm2"] = rnd(W, std=0.2)
+            sd[p + "mlp.router"] = rnd(E, W, std=(0.7 if calm else 3.0) * s)
+            for e in range(E):
+                sd[p + f"mlp.e{e}.gate"], sd[p + f"mlp.e{e}.up"] = rnd(ff, W, std=2 * s), rnd(ff, W, std=2 * s)
+                sd[p + f"mlp.e{e}.down"] = rnd(W, ff, std=ff ** -0.5)
+    return sd

@@ -132,9 +132,11 @@ __device__ __forceinline__ void sa_range(const SigmoidAttnParams& p, int ps, int
 
 template <typename CT>
 __global__ void __launch_bounds__(SA_THREADS) sigmoid_attn_kernel(SigmoidAttnParams p) {
+  // (everything in dynamic shared memory: with static arrays beside it the kernel could not be given the device's maximum)
   extern __shared__ __align__(16) float sa_sm[];
-  __shared__ long long key_off[SA_KEYS];      // element offset of the chunk's keys in their cache (per key/value head 0)
-  __shared__ int key_id[SA_KEYS];             // block index (pooled) or position (token); -1: none
+  long long* key_off = reinterpret_cast<long long*>(sa_sm);       // [SA_KEYS] element offset of the chunk's keys in their cache
+  int* key_id = reinterpret_cast<int*>(key_off + SA_KEYS);        // [SA_KEYS] block index (pooled) or position (token); -1: none
+  float* sa_data = reinterpret_cast<float*>(key_id + SA_KEYS);
   pdl_sync();
   const int R = p.H / p.G;
   const int hc_n = (R + p.heads_per_cta - 1) / p.heads_per_cta;
@@ -154,7 +156,7 @@ __global__ void __launch_bounds__(SA_THREADS) sigmoid_attn_kernel(SigmoidAttnPar
   }
   if (nrows <= 0) return;
   const int pairs = nrows * nh, D = p.dim, V = p.vdim, ldk = D + 1;
-  float* qs = sa_sm;                                   // [pairs][D]
+  float* qs = sa_data;                                 // [pairs][D]
   float* acc = qs + SA_ROWS * p.heads_per_cta * D;     // [pairs][V]
   float* ks = acc + SA_ROWS * p.heads_per_cta * V;     // [SA_KEYS][D + 1]
   float* vs = ks + SA_KEYS * ldk;                      // [SA_KEYS][V]
@@ -347,7 +349,8 @@ int vb_sigmoid_attn(void* d_out, int ld_out, const void* d_q, const void* d_k_ca
   SigmoidAttnParams p{d_q, d_k_cache, d_v_cache, d_kp, d_vp, d_head_bias, d_out, ld_out, d_part, d_row_req, d_pos, d_page_indptr,
                       d_page_indices, d_qo_indptr, d_tile_req, d_tile_row0, d_row_list, items, H, G, dim, vdim, page_size, window,
                       pool, pool > 0 ? (page_size + pool - 1) / pool : 0, scale, cap, out_scale, tile_rows, hpc, 1};
-  const size_t smem = (static_cast<size_t>(SA_ROWS) * hpc * (dim + vdim) + static_cast<size_t>(SA_KEYS) * (dim + 1 + vdim)) * sizeof(float);
+  const size_t smem = (static_cast<size_t>(SA_ROWS) * hpc * (dim + vdim) + static_cast<size_t>(SA_KEYS) * (dim + 1 + vdim)) * sizeof(float) +
+                      SA_KEYS * (sizeof(long long) + sizeof(int));
   VB_CHECK_ARG(smem <= static_cast<size_t>(VB_MAX_DYN_SMEM), "vb_sigmoid_attn: head sizes need %zu bytes of shared memory", smem);
   const int gy = G * ((R + hpc - 1) / hpc);
   // single rows of a small step: a row's key chunks dealt to several CTAs (partial planes, summed in order afterwards)

@@ -547,7 +547,7 @@ class HybridWeights:
                     tuple(sd[rp + "A_log"].shape) != (r.inner, r.state)):
                 raise VoxB200Error(f"layer {i}: selective-scan shapes do not match the configuration")
             w["in"] = dense(torch.cat([q, k, v, xin], 0).contiguous())
-            if a.conv > 1:
+            if a.conv >= 1:
                 w["qkv_conv"] = torch.cat([vec(lp + n + ".conv") for n in ("q", "k", "v")], 0).contiguous()
                 if tuple(w["qkv_conv"].shape) != (nq + nk + nv, a.conv):
                     raise VoxB200Error(f"layer {i}: short convolution shapes do not match the configuration")
@@ -773,9 +773,9 @@ class HybridCache:
                     per_page = (page_size + a.pool - 1) // a.pool
                     self.k_pool[i] = torch.zeros(num_pages, per_page, a.kv_heads, a.dim, dtype=F32, device=device)
                     self.v_pool[i] = torch.zeros(num_pages, per_page, a.kv_heads, a.vdim, dtype=F32, device=device)
-                if a.conv > 1:
+                if a.conv >= 1:
                     n = a.heads * a.dim + a.kv_heads * (a.dim + a.vdim)
-                    self.conv[(i, "qkv")] = torch.zeros(num_slots, a.conv - 1, n, dtype=F32, device=device)
+                    self.conv[(i, "qkv")] = torch.zeros(num_slots, max(a.conv - 1, 1), n, dtype=F32, device=device)
                 self.conv[(i, "x")] = torch.zeros(num_slots, max(r.conv - 1, 1), r.inner, dtype=F32, device=device)
                 self.state[i] = torch.zeros(num_slots, r.inner, r.state, dtype=F32, device=device)
             else:
@@ -1444,7 +1444,7 @@ class HybridEngine:
         conv_args = (s.qo_indptr, s.row_req, s.pos, s.slots, s.B)
         # ---- left: convolutions, whole-projection norms, append, pooled blocks, attention ----
         qkv = proj[:, :nqkv]
-        if a.conv > 1:
+        if a.conv >= 1:
             qkv2 = self.proj2[:T * nqkv].view(T, nqkv)
             ops.short_conv(qkv, w["qkv_conv"], None, cache.conv[(i, "qkv")], *conv_args, out_f32=qkv2)
             qkv = qkv2

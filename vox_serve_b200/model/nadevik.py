@@ -28,7 +28,7 @@ request's slot of ``HybridCache``.  Everything a model of this design can vary i
 """
 from __future__ import annotations
 
-from typing import Any, Dict, Optional
+from typing import Any, Dict
 
 import torch
 
@@ -130,7 +130,7 @@ def synthetic_state_dict(cfg: HybridConfig, seed: int = 0, device="cpu") -> Dict
             nq, nk, nv = a.heads * a.dim, a.kv_heads * a.dim, a.kv_heads * a.vdim
             sd[lp + "q"], sd[lp + "k"], sd[lp + "v"] = rnd(nq, W, std=s), rnd(nk, W, std=s), rnd(nv, W, std=s)
             sd[lp + "q.norm"], sd[lp + "k.norm"] = rnd(nq, std=0.1, mean=1.0), rnd(nk, std=0.1, mean=1.0)
-            if a.conv > 1:
+            if a.conv >= 1:
                 for n, c in (("q", nq), ("k", nk), ("v", nv)):
                     sd[lp + n + ".conv"] = rnd(c, a.conv, std=0.5)
             sd[lp + "pb"] = rnd(a.heads, std=0.5, mean=-2.0)
