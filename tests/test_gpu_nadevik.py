@@ -299,7 +299,7 @@ def test_bfloat16_tensor_core_sizes():
     plain = _replay(_worker(cfg, sd, BF16, slots=2, pages=24, page_size=64, max_rows=1024, tensor_core_projections=False),
                     {"a": toks}, [[("a", 600)]])["a"]
     assert _err50(whole, plain.double()) < 3e-2 and _err50(parts, plain.double()) < 3e-2
-    assert _err50(plain, ref) < 0.2 and _err50(whole[:40], ref[:40]) < TOL[BF16]
+    assert _err50(plain, ref) < 0.2 and _err50(whole[:40], ref[:40]) < 0.15
     w32 = _worker(cfg, sd, F32, slots=2, pages=24, page_size=64, max_rows=1024)
     assert _err(_replay(w32, {"a": toks}, [[("a", 600)]])["a"], ref) < TOL[F32]
     w32.engine.use_tiled_recurrence = w32.engine.use_tiled_attention = False
@@ -405,43 +405,56 @@ def test_sigmoid_attention_window_and_pool_edges(dtype, window, pool, page):
 
 
 @pytest.mark.gpu
-def test_sigmoid_attention_far_keys_batches_and_out_scale():
+@pytest.mark.parametrize("dtype,H,G,D,V", [(F32, 10, 2, 24, 40), (BF16, 10, 2, 24, 40), (BF16, 8, 2, 32, 48), (BF16, 6, 3, 64, 128),
+                                           (BF16, 3, 3, 16, 16), (BF16, 4, 1, 128, 64)])
+def test_sigmoid_attention_far_keys_batches_and_out_scale(dtype, H, G, D, V):
     """three requests of unequal lengths in one launch (tiles and single rows), positions hundreds of keys and dozens of pages
-    from their hot key, an output scale, larger heads per group than a CTA takes at once"""
+    from their hot key, an output scale, more heads per group than a CTA takes at once; the plain kernel (float32, odd sizes)
+    and the tensor-core tiles (bfloat16, head sizes in multiples of 16) with one, two and four heads per key/value head"""
     from vox_serve_b200 import ops
 
     torch.manual_seed(2)
-    H, G, D, V, page, window, pool = 10, 2, 24, 40, 8, 50, 6
+    page, window, pool = 8, 50, 6
     lens = [300, 1, 77]
     seqs = []
     for n in lens:
         q, k, v = torch.randn(n, H, D, dtype=F64) * 0.05, torch.randn(n, G, D, dtype=F64) * 0.05, torch.randn(n, G, V, dtype=F64)
         k[min(3, n - 1), :, 1] = 7.0 * pool
         q[:, :, 1] = 3.0
-        seqs.append((q, k, v))
+        seqs.append(tuple(t.to(dtype).to(F64) for t in (q, k, v)))
     bias = torch.full((H,), -12.0, dtype=F64)
     indptr, pages, n_pages = _paged(lens, page, seed=5)
-    kc = torch.zeros(n_pages, page, G, D, dtype=F32, device=DEV)
-    vc = torch.zeros(n_pages, page, G, V, dtype=F32, device=DEV)
+    kc = torch.zeros(n_pages, page, G, D, dtype=dtype, device=DEV)
+    vc = torch.zeros(n_pages, page, G, V, dtype=dtype, device=DEV)
     per = (page + pool - 1) // pool
     kp, vp = torch.zeros(n_pages, per, G, D, dtype=F32, device=DEV), torch.zeros(n_pages, per, G, V, dtype=F32, device=DEV)
     T = sum(lens)
     qo, row_req, pos = _step_tables([(0, n) for n in lens])
     proj = torch.cat([torch.cat([t.reshape(n, -1) for t in s], 1) for s, n in zip(seqs, lens)], 0).to(F32).to(DEV).contiguous()
-    qd = torch.zeros(T, H * D, dtype=F32, device=DEV)
+    qd = torch.zeros(T, H * D, dtype=dtype, device=DEV)
     ops.qk_norm_append(proj, 0, H * D, H * D + G * D, None, None, 1e-5, qd, kc, vc, row_req, pos, indptr, pages, T)
     ops.pool_blocks(kp, vp, kc, vc, pool, qo, pos, indptr, pages, T, 3)
-    out = torch.zeros(T, H * V, dtype=F32, device=DEV)
+    out = torch.zeros(T, H * V + 2, dtype=dtype, device=DEV)
     tile_rows = ops.window_attn_tile_rows()
     tiles = [(b, r) for b, n in enumerate(lens) if n > 1 for r in range(int(qo[b]), int(qo[b]) + n, tile_rows)]
     tr = torch.tensor([b for b, _ in tiles], dtype=I32, device=DEV)
     t0 = torch.tensor([r for _, r in tiles], dtype=I32, device=DEV)
-    args = (qd, kc, vc, kp, vp, bias.to(F32).to(DEV), out, row_req, pos, indptr, pages, T, H, window, pool, 0.8, 0.0, 0.6)
+    args = (qd, kc, vc, kp, vp, bias.to(F32).to(DEV), out[:, :H * V], row_req, pos, indptr, pages, T, H, window, pool, 0.8, 0.0, 0.6)
     ops.sigmoid_attn(*args, tiles=(qo, tr, t0, len(tiles), tile_rows))
     ops.sigmoid_attn(*args, rows=(torch.tensor([300], dtype=I32, device=DEV), 1))
     ref = torch.cat([0.6 * O.sigmoid_attend(q, k, v, bias, 0.8, 0.0, window, pool).reshape(n, -1) for (q, k, v), n in zip(seqs, lens)], 0)
     assert ref[299].abs().max() > 1e-2                       # position 299 still sees its hot key, through block 0
-    assert (out.double().cpu() - ref).abs().max().item() < 1e-5 * max(1.0, ref.abs().max().item())
+    tol = (1e-5 if dtype == F32 else 2e-2) * max(1.0, ref.abs().max().item())
+    assert (out[:, :H * V].double().cpu() - ref).abs().max().item() < tol and (out[:, H * V:] == 0).all()
+    # rows as single-token rows: all of them, and a few with their keys dealt to several CTAs
+    out2 = torch.zeros(T, H * V, dtype=dtype, device=DEV)
+    ops.sigmoid_attn(*args[:6], out2, *args[7:])
+    assert (out2.double().cpu() - ref).abs().max().item() < tol
+    few = [299, 150, 377, 300, 60]
+    out3 = torch.zeros(T, H * V, dtype=dtype, device=DEV)
+    ops.sigmoid_attn(*args[:6], out3, *args[7:], rows=(torch.tensor(few, dtype=I32, device=DEV), len(few)),
+                     scratch=torch.zeros(1 << 22, dtype=F32, device=DEV), max_keys=4096)
+    assert (out3[few].double().cpu() - ref[few]).abs().max().item() < tol and out3.abs().sum() == out3[few].abs().sum()
 
 
 @pytest.mark.gpu

@@ -270,6 +270,189 @@ __global__ void __launch_bounds__(SA_THREADS) sigmoid_attn_kernel(SigmoidAttnPar
   }
 }
 
+// ---- the same on tensor-core tiles (bf16, head sizes in multiples of 16, values up to 128 per head) ---------------------------
+// CTA = 4 warps = 64 query rows: 64 / nh rows of a prompt portion's tile times nh = 1 / 2 / 4 heads of one key/value head (warp w
+// holds 16 token rows of one head), or -- single-token rows -- one token's heads (one row per warp in use).  Chunks of 64 keys
+// (pooled blocks, rounded to bf16 here, then tokens) are staged once for all of them; S = Q K^T by mma.sync m16n8k16 with fp32
+// accumulators, the weights sigmoid(cap(S) + bias) are formed on the accumulator fragments, masked, rounded to bf16 and fed
+// back as the A operand of O += P V (values read through transposing ldmatrix).
+constexpr int SM_KEYS = 64;
+
+template <int NV>
+__global__ void __launch_bounds__(128) sigmoid_attn_mma_kernel(SigmoidAttnParams p) {
+  extern __shared__ __align__(16) unsigned char sm_raw[];
+  using bf16 = __nv_bfloat16;
+  const int D = p.dim, V = p.vdim, QLD = D + 8, VLD = V + 8, D8 = D / 8, V8 = V / 8;
+  bf16* Qs = reinterpret_cast<bf16*>(sm_raw);                     // [64][QLD]
+  bf16* Ks = Qs + 64 * QLD;                                       // [SM_KEYS][QLD]
+  bf16* Vs = Ks + SM_KEYS * QLD;                                  // [SM_KEYS][VLD]
+  long long* key_off = reinterpret_cast<long long*>(Vs + SM_KEYS * VLD);
+  int* key_id = reinterpret_cast<int*>(key_off + SM_KEYS);
+  pdl_sync();
+  const int R = p.H / p.G, nh = p.heads_per_cta, wph = 4 / nh;    // warps per head
+  const int hc_n = (R + nh - 1) / nh;
+  const int g = blockIdx.y / hc_n, hc = blockIdx.y - g * hc_n;
+  const int h0 = g * R + hc * nh, nh_eff = min(nh, R - hc * nh), TR = 16 * wph;
+  int b, row0, nrows;
+  const int item_row = blockIdx.x;
+  if (p.tile_req) {
+    const int sub_n = p.tile_rows / TR, tile = blockIdx.x / sub_n, sub = blockIdx.x - tile * sub_n;
+    b = p.tile_req[tile];
+    const int t0 = p.tile_row0[tile], end = min(p.qo_indptr[b + 1], t0 + p.tile_rows);
+    row0 = t0 + sub * TR;
+    nrows = min(TR, end - row0);
+  } else {
+    row0 = p.row_list ? p.row_list[blockIdx.x] : blockIdx.x;
+    b = p.row_req[row0];
+    nrows = 1;
+  }
+  if (nrows <= 0) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int my_h = warp / wph, my_rb = (warp - my_h * wph) * 16;   // this warp's head and first token row
+  const bool active = my_h < nh_eff && my_rb < nrows;
+  const bf16* q = static_cast<const bf16*>(p.q);
+  for (int i = tid; i < 64 * D8; i += 128) {
+    const int pr = i / D8, c = (i - pr * D8) * 8, w_ = pr >> 4, hh = w_ / wph, r = (w_ - hh * wph) * 16 + (pr & 15);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (hh < nh_eff && r < nrows) v = *reinterpret_cast<const uint4*>(q + (static_cast<size_t>(row0 + r) * p.H + h0 + hh) * D + c);
+    *reinterpret_cast<uint4*>(Qs + pr * QLD + c) = v;
+  }
+  float O[2 * NV][4];
+#pragma unroll
+  for (int n = 0; n < 2 * NV; ++n) O[n][0] = O[n][1] = O[n][2] = O[n][3] = 0.f;
+  const int p_first = p.pos[row0], p_last = p_first + nrows - 1;
+  int nb_max, lo_last, nb_first, lo_first;
+  sa_range(p, p_last, nb_max, lo_last);
+  sa_range(p, p_first, nb_first, lo_first);
+  const int n_items = nb_max + (p_last - lo_first + 1);
+  int it0 = 0, it1 = n_items;
+  if (p.splits > 1) {
+    const int chunks = (n_items + SM_KEYS - 1) / SM_KEYS, per = (chunks + p.splits - 1) / p.splits;
+    it0 = min(n_items, static_cast<int>(blockIdx.z) * per * SM_KEYS);
+    it1 = min(n_items, it0 + per * SM_KEYS);
+  }
+  const int32_t* pages = p.page_indices + p.page_indptr[b];
+  const bf16* kc = static_cast<const bf16*>(p.k_cache);
+  const bf16* vc = static_cast<const bf16*>(p.v_cache);
+  const float bias = (p.head_bias && my_h < nh_eff) ? p.head_bias[h0 + my_h] : 0.f;
+  const int ra = my_rb + (lane >> 2), psa = p_first + ra, psb = psa + 8;
+  int nba, loa, nbb, lob;
+  sa_range(p, psa, nba, loa);
+  sa_range(p, psb, nbb, lob);
+  const bool va = ra < nrows, vb_ = ra + 8 < nrows;
+  for (int c0 = it0; c0 < it1; c0 += SM_KEYS) {
+    __syncthreads();
+    if (tid < SM_KEYS) {
+      const int it = c0 + tid;
+      int id = -1;
+      long long off = 0;
+      if (it < it1) {
+        if (it < nb_max) {
+          id = it;
+          const int first = it * p.pool;
+          off = static_cast<long long>(pages[first / p.page_size]) * p.pool_slots + (first % p.page_size) / p.pool;
+        } else {
+          id = lo_first + it - nb_max;
+          off = static_cast<long long>(pages[id / p.page_size]) * p.page_size + id % p.page_size;
+        }
+      }
+      key_id[tid] = id;
+      key_off[tid] = off;
+    }
+    __syncthreads();
+    for (int i = tid; i < SM_KEYS * (D8 + V8); i += 128) {
+      const int kk = i / (D8 + V8), j = i - kk * (D8 + V8);
+      const bool is_k = j < D8;
+      const int c = (is_k ? j : j - D8) * 8, n = is_k ? D : V;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (key_id[kk] >= 0) {
+        const size_t e = (static_cast<size_t>(key_off[kk]) * p.G + g) * n + c;
+        if (c0 + kk < nb_max) {
+          const float* src = (is_k ? p.kp : p.vp) + e;
+          const float4 a = *reinterpret_cast<const float4*>(src), bq = *reinterpret_cast<const float4*>(src + 4);
+          v = make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(bq.x, bq.y), pack_bf16(bq.z, bq.w));
+        } else {
+          v = *reinterpret_cast<const uint4*>((is_k ? kc : vc) + e);
+        }
+      }
+      *reinterpret_cast<uint4*>((is_k ? Ks + kk * QLD : Vs + kk * VLD) + c) = v;
+    }
+    __syncthreads();
+    if (!active) continue;
+    float S[SM_KEYS / 8][4];
+#pragma unroll
+    for (int n = 0; n < SM_KEYS / 8; ++n) S[n][0] = S[n][1] = S[n][2] = S[n][3] = 0.f;
+    for (int kb = 0; kb < D / 16; ++kb) {
+      uint32_t af[4];
+      ldmatrix_x4(af, smem_u32(Qs + (warp * 16 + (lane & 15)) * QLD + kb * 16 + (lane >> 4) * 8));
+#pragma unroll
+      for (int np = 0; np < SM_KEYS / 16; ++np) {
+        uint32_t bf[4];
+        ldmatrix_x4(bf, smem_u32(Ks + (np * 16 + (lane >> 4) * 8 + (lane & 7)) * QLD + kb * 16 + ((lane >> 3) & 1) * 8));
+        mma_bf16_16816(S[2 * np], af, bf[0], bf[1]);
+        mma_bf16_16816(S[2 * np + 1], af, bf[2], bf[3]);
+      }
+    }
+    bool any = false;
+#pragma unroll
+    for (int nt = 0; nt < SM_KEYS / 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int col = nt * 8 + (lane & 3) * 2 + (e & 1);
+        const int id = key_id[col];
+        const bool pooled = c0 + col < nb_max, second = e >= 2;
+        const int ps = second ? psb : psa;
+        const bool seen = id >= 0 && (second ? vb_ : va) &&
+                          (pooled ? id < (second ? nbb : nba) : (id >= (second ? lob : loa) && id <= ps));
+        float w = 0.f;
+        if (seen) {
+          float sc = S[nt][e] * p.scale;
+          if (p.cap > 0.f) sc = p.cap * tanhf(sc / p.cap);
+          w = 1.f / (1.f + expf(-(sc + bias)));
+          any = true;
+        }
+        S[nt][e] = w;
+      }
+    }
+    if (!__any_sync(0xffffffffu, any)) continue;
+#pragma unroll
+    for (int kb = 0; kb < SM_KEYS / 16; ++kb) {
+      uint32_t a[4] = {pack_bf16(S[2 * kb][0], S[2 * kb][1]), pack_bf16(S[2 * kb][2], S[2 * kb][3]),
+                       pack_bf16(S[2 * kb + 1][0], S[2 * kb + 1][1]), pack_bf16(S[2 * kb + 1][2], S[2 * kb + 1][3])};
+#pragma unroll
+      for (int np = 0; np < NV; ++np) {
+        if (np * 16 < V) {
+          uint32_t bf[4];
+          ldmatrix_x4_trans(bf, smem_u32(Vs + (kb * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * VLD + np * 16 + (lane >> 4) * 8));
+          mma_bf16_16816(O[2 * np], a, bf[0], bf[1]);
+          mma_bf16_16816(O[2 * np + 1], a, bf[2], bf[3]);
+        }
+      }
+    }
+  }
+  if (!active) return;
+  const int h = h0 + my_h;
+#pragma unroll
+  for (int nt = 0; nt < 2 * NV; ++nt) {
+    const int v = nt * 8 + (lane & 3) * 2;
+    if (v >= V) continue;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = ra + 8 * half;
+      if (r >= nrows) continue;
+      const float o0 = O[nt][2 * half], o1 = O[nt][2 * half + 1];
+      if (p.splits > 1) {
+        float* part = p.part + (static_cast<size_t>(blockIdx.z) * p.n_items + item_row) * p.H * V + h * V + v;
+        part[0] = o0;
+        part[1] = o1;
+      } else {
+        bf16* out = static_cast<bf16*>(p.out) + static_cast<size_t>(row0 + r) * p.ld_out + h * V + v;
+        *reinterpret_cast<uint32_t*>(out) = pack_bf16(p.out_scale * o0, p.out_scale * o1);
+      }
+    }
+  }
+}
+
 // out[row] = out_scale * sum of the splits' partial planes, in split order
 template <typename CT>
 __global__ void sigmoid_attn_sum_kernel(CT* __restrict__ out, int ld_out, const float* __restrict__ part,
@@ -343,20 +526,29 @@ int vb_sigmoid_attn(void* d_out, int ld_out, const void* d_q, const void* d_k_ca
   const bool tiled = d_tile_req != nullptr;
   VB_CHECK_ARG(!tiled || (d_tile_row0 && d_qo_indptr && tile_rows > 0 && tile_rows % SA_ROWS == 0),
                "vb_sigmoid_attn: tiles of a multiple of %d rows", SA_ROWS);
-  const int items = tiled ? n_tiles * (tile_rows / SA_ROWS) : n_rows;
+  const int R = H / G;
+  // tensor-core tiles: bf16, head sizes in multiples of 16 (keys up to 256, values up to 128 dims), 4-byte aligned output rows
+  const bool mma = dtype == 0 && dim % 16 == 0 && vdim % 16 == 0 && vdim <= 128 && ld_out % 2 == 0 && (!tiled || tile_rows == 64) &&
+                   reinterpret_cast<uintptr_t>(d_out) % 4 == 0 && reinterpret_cast<uintptr_t>(d_q) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(d_k_cache) % 16 == 0 && reinterpret_cast<uintptr_t>(d_v_cache) % 16 == 0 &&
+                   (pool <= 0 || (reinterpret_cast<uintptr_t>(d_kp) % 16 == 0 && reinterpret_cast<uintptr_t>(d_vp) % 16 == 0));
+  const int hpc = mma ? (R >= 4 ? 4 : (R >= 2 ? 2 : 1)) : (R < 4 ? R : 4);
+  const int rows_per_cta = mma ? 64 / hpc : SA_ROWS, chunk_keys = mma ? SM_KEYS : SA_KEYS;
+  const int items = tiled ? n_tiles * (tile_rows / rows_per_cta) : n_rows;
   if (items <= 0) return 0;
-  const int R = H / G, hpc = R < 4 ? R : 4;
   SigmoidAttnParams p{d_q, d_k_cache, d_v_cache, d_kp, d_vp, d_head_bias, d_out, ld_out, d_part, d_row_req, d_pos, d_page_indptr,
                       d_page_indices, d_qo_indptr, d_tile_req, d_tile_row0, d_row_list, items, H, G, dim, vdim, page_size, window,
                       pool, pool > 0 ? (page_size + pool - 1) / pool : 0, scale, cap, out_scale, tile_rows, hpc, 1};
-  const size_t smem = (static_cast<size_t>(SA_ROWS) * hpc * (dim + vdim) + static_cast<size_t>(SA_KEYS) * (dim + 1 + vdim)) * sizeof(float) +
-                      SA_KEYS * (sizeof(long long) + sizeof(int));
+  const size_t smem = mma ? static_cast<size_t>(64 + SM_KEYS) * (dim + 8) * 2 + static_cast<size_t>(SM_KEYS) * (vdim + 8) * 2 +
+                                SM_KEYS * (sizeof(long long) + sizeof(int))
+                          : (static_cast<size_t>(SA_ROWS) * hpc * (dim + vdim) + static_cast<size_t>(SA_KEYS) * (dim + 1 + vdim)) * sizeof(float) +
+                                SA_KEYS * (sizeof(long long) + sizeof(int));
   VB_CHECK_ARG(smem <= static_cast<size_t>(VB_MAX_DYN_SMEM), "vb_sigmoid_attn: head sizes need %zu bytes of shared memory", smem);
   const int gy = G * ((R + hpc - 1) / hpc);
   // single rows of a small step: a row's key chunks dealt to several CTAs (partial planes, summed in order afterwards)
   int splits = 1;
   if (!tiled && d_part && max_keys > 0) {
-    const int chunks = (max_keys + SA_KEYS - 1) / SA_KEYS;
+    const int chunks = (max_keys + chunk_keys - 1) / chunk_keys;
     int want = 296 / (items * gy > 0 ? items * gy : 1);
     if (want > 16) want = 16;
     if (want > chunks / 2) want = chunks / 2;
@@ -365,7 +557,18 @@ int vb_sigmoid_attn(void* d_out, int ld_out, const void* d_q, const void* d_k_ca
   }
   p.splits = splits;
   dim3 grid(items, gy, splits);
-  if (dtype == 1) {
+  if (mma) {
+    if (vdim <= 32) {
+      if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(sigmoid_attn_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+      VB_LAUNCH_PDL(sigmoid_attn_mma_kernel<2>, grid, 128, smem, stream, p);
+    } else if (vdim <= 64) {
+      if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(sigmoid_attn_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+      VB_LAUNCH_PDL(sigmoid_attn_mma_kernel<4>, grid, 128, smem, stream, p);
+    } else {
+      if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(sigmoid_attn_mma_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
+      VB_LAUNCH_PDL(sigmoid_attn_mma_kernel<8>, grid, 128, smem, stream, p);
+    }
+  } else if (dtype == 1) {
     if (smem > 48 * 1024) VB_CHECK_CUDA(cudaFuncSetAttribute(sigmoid_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, VB_MAX_DYN_SMEM));
     VB_LAUNCH_PDL(sigmoid_attn_kernel<float>, grid, SA_THREADS, smem, stream, p);
   } else {
