@@ -509,7 +509,7 @@ def test_selective_scan_slots_pieces_and_portions():
     from vox_serve_b200 import ops
 
     tile_rows = ops.window_attn_tile_rows()
-    for inner, N, seed in ((40, 5, 0), (16, 1, 1), (24, 20, 2), (50, 40, 3), (8, 70, 4)):
+    for inner, N, seed in ((40, 5, 0), (16, 1, 1), (24, 20, 2), (50, 40, 3), (8, 70, 4), (200, 16, 5), (130, 12, 6)):
         g = torch.Generator().manual_seed(seed)
         lens = [150, 1, 37, 2, 70]
         A = -(torch.rand(inner, N, generator=g, dtype=F64) * 3 + 0.05)
@@ -563,10 +563,13 @@ def test_short_convolution_state_first_tokens_and_reuse():
     on slots that hold NaNs; the first tokens of a sequence see zeros, whatever the slot held"""
     from vox_serve_b200 import ops
 
-    for taps, C, act, res, bias in ((4, 37, "silu", False, True), (3, 256, None, True, False), (1, 5, None, False, False),
-                                    (2, 300, "silu", True, True), (6, 40, None, False, True)):
+    for taps, C, act, res, bias, lens in ((4, 37, "silu", False, True, [23, 1, 9]), (3, 256, None, True, False, [23, 1, 9]),
+                                          (1, 5, None, False, False, [23, 1, 9]), (2, 300, "silu", True, True, [23, 1, 9]),
+                                          (6, 40, None, False, True, [23, 1, 9]),
+                                          # long steps: several rows per thread
+                                          (4, 70, "silu", False, True, [150, 1, 67]), (3, 33, None, True, False, [90, 2, 131]),
+                                          (2, 20, None, False, True, [23, 100, 9])):
         g = torch.Generator().manual_seed(taps)
-        lens = [23, 1, 9]
         w = torch.randn(C, taps, generator=g, dtype=F64)
         bv = torch.randn(C, generator=g, dtype=F64) if bias else None
         xs = [torch.randn(n, C, generator=g, dtype=F64) for n in lens]
@@ -575,12 +578,14 @@ def test_short_convolution_state_first_tokens_and_reuse():
             y = O.causal_conv(x, w, bv)
             y = O.silu(y) if act else y
             ref.append(y + x if res else y)
-        for cuts in ([1000], [1] * 23, [2, 1, 3, 1000], [5, 5, 5, 1000], [1, 22]):
+        for cuts in ([1000], [1] * 23 + [1000], [2, 1, 3, 1000], [5, 5, 5, 1000], [1, 1000], [66, 3, 1000]):
             state = torch.full((5, max(taps - 1, 1), C), float("nan"), dtype=F32, device=DEV)
             slots = torch.tensor([3, 0, 4], dtype=I32, device=DEV)
             at, outs = [0] * 3, [[] for _ in lens]
             for c in cuts:
                 live = [(b, min(c, lens[b] - at[b])) for b in range(3) if at[b] < lens[b]]
+                if not live:
+                    break
                 qo, row_req, pos = _step_tables([(at[b], n) for b, n in live])
                 T = int(qo[-1])
                 wide = torch.full((T, C + 7), float("nan"), dtype=F32, device=DEV)

@@ -10,8 +10,10 @@
 // Everything is fp32; only `out` takes the compute type (it feeds the output projection).  A slot's stored state is ignored
 // when the request's first row of the step has position 0, so slots are handed out again without clearing.
 //
-// Eight lanes share a channel, each holding every eighth state in registers; a CTA of 128 threads walks a request's rows in
-// order for 16 channels, with the next row's operands already loaded while the current row's chain runs.
+// Up to 16 states per channel: a thread owns a channel and all its states; a CTA of 128 channels walks rows in blocks of 16 whose
+// B | C it stages in shared memory once and whose dt / x / z every thread loads up front (all in flight before the dependent
+// chain starts).  More states: eight lanes share a channel, each holding every eighth state in registers, with the next row's
+// operands already loaded while the current row's chain runs.
 //
 //   vb_selective_scan        every request of the step, rows in order (single tokens and portions)
 //   vb_selective_scan_tiled  prompt portions cut into pieces of rows: the recurrence composes as S_end = P * S_start + L with
@@ -201,13 +203,25 @@ __global__ void __launch_bounds__(128) scan_piece_carry_kernel(ScanParams p) {
   float* st = p.state + (static_cast<size_t>(p.slots[b]) * p.inner + ch) * p.N + s;
   float S = p.pos[r0] == 0 ? 0.f : *st;
   const float A = p.A[static_cast<size_t>(ch) * p.N + s];
-  for (int k = 0; k < n_pieces; ++k) {
-    const int tile = first + k / per * 1, j = k % per;
-    float* sc = p.scratch + ((static_cast<size_t>(tile) * per + j) * p.inner + ch) * (p.N + 1);
-    const float L = sc[s], sdt = sc[p.N];
-    __syncwarp();
-    sc[s] = S;
-    S = fmaf(expf(A * sdt), S, L);
+  // (a request's pieces are consecutive summary slots: its tiles are consecutive and whole but for the last)
+  float* sc0 = p.scratch + ((static_cast<size_t>(first) * per) * p.inner + ch) * (p.N + 1);
+  const size_t stride = static_cast<size_t>(p.inner) * (p.N + 1);
+  for (int k0 = 0; k0 < n_pieces; k0 += 8) {
+    float L[8], sd[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {                    // independent loads first, the dependent chain after
+      if (k0 + j < n_pieces) {
+        L[j] = sc0[(k0 + j) * stride + s];
+        sd[j] = sc0[(k0 + j) * stride + p.N];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (k0 + j < n_pieces) {
+        sc0[(k0 + j) * stride + s] = S;
+        S = fmaf(expf(A * sd[j]), S, L[j]);
+      }
+    }
   }
   *st = S;
 }
@@ -249,7 +263,151 @@ static int launch_scan(const ScanParams& p, int out_dtype, bool tiled, cudaStrea
   return 0;
 }
 
+
+// ---- a thread per channel (up to 16 states) ---------------------------------------------------------------------------------
+constexpr int S1_ROWS = 16;          // rows walked per staged block
+constexpr int S1_THREADS = 128;
+
+template <typename CT, int NM, bool WRITE>
+__device__ __forceinline__ void ss_walk1(const ScanParams& p, int ch, bool valid, int r0, int r1, float (&S)[NM],
+                                         const float (&A)[NM], float* sum_dt, float* bc_sm) {
+  const float bias = p.dt_bias ? p.dt_bias[ch] : 0.f;
+  const float Dc = p.Dv ? p.Dv[ch] : 0.f;
+  float sdt = 0.f;
+  for (int rb = r0; rb < r1; rb += S1_ROWS) {
+    const int nr = min(S1_ROWS, r1 - rb);
+    __syncthreads();                                   // the block before is consumed
+    for (int i = threadIdx.x; i < nr * 2 * NM; i += S1_THREADS) {
+      const int r = i / (2 * NM), j = i - r * 2 * NM, n = j < NM ? j : j - NM;
+      bc_sm[i] = n < p.N ? p.bc[static_cast<size_t>(rb + r) * p.ld_bc + (j < NM ? p.b_off : p.c_off) + n] : 0.f;
+    }
+    float dtr[S1_ROWS], xr[S1_ROWS], zr[S1_ROWS];
+#pragma unroll
+    for (int r = 0; r < S1_ROWS; ++r) {
+      if (r < nr) {
+        dtr[r] = p.dt[static_cast<size_t>(rb + r) * p.ld_dt + ch];
+        xr[r] = p.x[static_cast<size_t>(rb + r) * p.ld_x + ch];
+        if (WRITE) zr[r] = p.z[static_cast<size_t>(rb + r) * p.ld_z + ch];
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < S1_ROWS; ++r) {
+      if (r < nr) {
+        const float dtv = ss_softplus(dtr[r] + bias), xv = xr[r];
+        sdt += dtv;
+        const float dx = dtv * xv;
+        const float* row = bc_sm + r * 2 * NM;
+        float y = 0.f;
+#pragma unroll
+        for (int n = 0; n < NM; ++n) {
+          S[n] = fmaf(expf(dtv * A[n]), S[n], dx * row[n]);
+          if (WRITE) y = fmaf(S[n], row[NM + n], y);
+        }
+        if (WRITE && valid) {
+          const float zv = zr[r];
+          y = fmaf(Dc, xv, y);
+          ss_store<CT>(p.out, static_cast<size_t>(rb + r) * p.ld_out + ch, p.out_scale * y * (zv / (1.f + expf(-zv))));
+        }
+      }
+    }
+  }
+  if (sum_dt) *sum_dt = sdt;
+}
+
+template <int NM>
+__device__ __forceinline__ void ss_load_A1(const ScanParams& p, int ch, float (&A)[NM]) {
+#pragma unroll
+  for (int n = 0; n < NM; ++n) A[n] = n < p.N ? p.A[static_cast<size_t>(ch) * p.N + n] : 0.f;
+}
+
+template <typename CT, int NM>
+__global__ void __launch_bounds__(S1_THREADS) selective_scan1_kernel(ScanParams p) {
+  __shared__ float bc_sm[S1_ROWS * 2 * NM];
+  pdl_sync();
+  const int b = blockIdx.y;
+  int ch = blockIdx.x * S1_THREADS + threadIdx.x;
+  const bool valid = ch < p.inner;
+  if (!valid) ch = p.inner - 1;
+  const int r0 = p.qo_indptr[b], r1 = p.qo_indptr[b + 1];
+  const int n = r1 - r0;
+  if (n <= 0 || (n == 1 && !p.single_rows) || (n > 1 && !p.multi_rows)) return;
+  float* st = p.state + (static_cast<size_t>(p.slots[b]) * p.inner + ch) * p.N;
+  float S[NM], A[NM];
+  ss_load_A1<NM>(p, ch, A);
+  const bool fresh = p.pos[r0] == 0;
+#pragma unroll
+  for (int i = 0; i < NM; ++i) S[i] = (!fresh && i < p.N) ? st[i] : 0.f;
+  ss_walk1<CT, NM, true>(p, ch, valid, r0, r1, S, A, nullptr, bc_sm);
+  if (valid) {
+#pragma unroll
+    for (int i = 0; i < NM; ++i)
+      if (i < p.N) st[i] = S[i];
+  }
+}
+
+template <int NM>
+__global__ void __launch_bounds__(S1_THREADS) scan1_piece_sum_kernel(ScanParams p) {
+  __shared__ float bc_sm[S1_ROWS * 2 * NM];
+  pdl_sync();
+  const int piece = blockIdx.y;
+  int ch = blockIdx.x * S1_THREADS + threadIdx.x;
+  const bool valid = ch < p.inner;
+  if (!valid) ch = p.inner - 1;
+  int b, r0, r1;
+  if (!ss_piece_rows(p, piece, b, r0, r1)) return;
+  float S[NM], A[NM], sdt;
+  ss_load_A1<NM>(p, ch, A);
+#pragma unroll
+  for (int i = 0; i < NM; ++i) S[i] = 0.f;
+  ss_walk1<float, NM, false>(p, ch, valid, r0, r1, S, A, &sdt, bc_sm);
+  if (!valid) return;
+  float* sc = p.scratch + (static_cast<size_t>(piece) * p.inner + ch) * (p.N + 1);
+#pragma unroll
+  for (int i = 0; i < NM; ++i)
+    if (i < p.N) sc[i] = S[i];
+  sc[p.N] = sdt;
+}
+
+template <typename CT, int NM>
+__global__ void __launch_bounds__(S1_THREADS) scan1_piece_out_kernel(ScanParams p) {
+  __shared__ float bc_sm[S1_ROWS * 2 * NM];
+  pdl_sync();
+  const int piece = blockIdx.y;
+  int ch = blockIdx.x * S1_THREADS + threadIdx.x;
+  const bool valid = ch < p.inner;
+  if (!valid) ch = p.inner - 1;
+  int b, r0, r1;
+  if (!ss_piece_rows(p, piece, b, r0, r1)) return;
+  float S[NM], A[NM];
+  ss_load_A1<NM>(p, ch, A);
+  const float* sc = p.scratch + (static_cast<size_t>(piece) * p.inner + ch) * (p.N + 1);
+#pragma unroll
+  for (int i = 0; i < NM; ++i) S[i] = i < p.N ? sc[i] : 0.f;
+  ss_walk1<CT, NM, true>(p, ch, valid, r0, r1, S, A, nullptr, bc_sm);
+}
+
+template <int NM>
+static int launch_scan1(const ScanParams& p, int out_dtype, bool tiled, cudaStream_t stream) {
+  const int cx = (p.inner + S1_THREADS - 1) / S1_THREADS;
+  if (!tiled) {
+    if (out_dtype == 1) VB_LAUNCH_PDL((selective_scan1_kernel<float, NM>), dim3(cx, p.B), S1_THREADS, 0, stream, p);
+    else VB_LAUNCH_PDL((selective_scan1_kernel<__nv_bfloat16, NM>), dim3(cx, p.B), S1_THREADS, 0, stream, p);
+    return 0;
+  }
+  const int pieces = p.n_tiles * (p.tile_rows / p.piece_rows);
+  const long long states = static_cast<long long>(p.inner) * p.N;
+  VB_LAUNCH_PDL(scan1_piece_sum_kernel<NM>, dim3(cx, pieces), S1_THREADS, 0, stream, p);
+  VB_LAUNCH_PDL(scan_piece_carry_kernel, dim3(static_cast<unsigned>((states + 127) / 128), p.B), 128, 0, stream, p);
+  if (out_dtype == 1) VB_LAUNCH_PDL((scan1_piece_out_kernel<float, NM>), dim3(cx, pieces), S1_THREADS, 0, stream, p);
+  else VB_LAUNCH_PDL((scan1_piece_out_kernel<__nv_bfloat16, NM>), dim3(cx, pieces), S1_THREADS, 0, stream, p);
+  return 0;
+}
+
 static int dispatch_scan(const ScanParams& p, int out_dtype, bool tiled, cudaStream_t stream) {
+  if (p.N <= 4) return launch_scan1<4>(p, out_dtype, tiled, stream);
+  if (p.N <= 8) return launch_scan1<8>(p, out_dtype, tiled, stream);
+  if (p.N <= 16) return launch_scan1<16>(p, out_dtype, tiled, stream);
   const int npl = (p.N + SS_LANES - 1) / SS_LANES;
   if (npl <= 1) return launch_scan<1>(p, out_dtype, tiled, stream);
   if (npl <= 2) return launch_scan<2>(p, out_dtype, tiled, stream);

@@ -68,6 +68,45 @@ __global__ void __launch_bounds__(256) short_conv_kernel(ShortConvParams p) {
   if (p.out_f32) p.out_f32[static_cast<size_t>(t) * p.ld_f32 + c] = acc;
 }
 
+// Long steps, 2 to 4 taps: a thread computes SC_RPT consecutive rows of its channel from one read of the rows' inputs (the
+// taps of neighbouring rows overlap), with the same FMA chain per output as the kernel above.
+constexpr int SC_RPT = 8;
+
+template <typename CT, int TAPS>
+__global__ void __launch_bounds__(256) short_conv_rows_kernel(ShortConvParams p) {
+  pdl_sync();
+  const int c = blockIdx.x * 256 + threadIdx.x, t0 = blockIdx.y * SC_RPT;
+  if (c >= p.C) return;
+  constexpr int K = TAPS - 1;
+  float u[SC_RPT + K], w[TAPS];
+#pragma unroll
+  for (int i = 0; i < SC_RPT + K; ++i) {
+    const int t = t0 - K + i;
+    u[i] = (t >= 0 && t < p.T) ? p.in[static_cast<size_t>(t) * p.ld_in + c] : 0.f;
+  }
+#pragma unroll
+  for (int j = 0; j < TAPS; ++j) w[j] = p.w[static_cast<size_t>(c) * TAPS + j];
+  const float bias = p.bias ? p.bias[c] : 0.f;
+#pragma unroll
+  for (int rr = 0; rr < SC_RPT; ++rr) {
+    const int t = t0 + rr;
+    if (t < p.T) {
+      const int b = p.row_req[t], r = t - p.qo_indptr[b], ps = p.pos[t];
+      const float* st = p.state + (static_cast<size_t>(p.slots[b]) * K) * p.C + c;
+      float acc = bias;
+#pragma unroll
+      for (int j = 0; j < TAPS; ++j) {
+        const int back = K - j;
+        if (ps - back >= 0) acc = fmaf(w[j], r - back >= 0 ? u[rr + j] : st[static_cast<size_t>(r + j) * p.C], acc);
+      }
+      if (p.act == 1) acc = acc / (1.f + expf(-acc));
+      if (p.residual) acc += u[rr + K];
+      if (p.out) sc_store<CT>(p.out, static_cast<size_t>(t) * p.ld_out + c, acc);
+      if (p.out_f32) p.out_f32[static_cast<size_t>(t) * p.ld_f32 + c] = acc;
+    }
+  }
+}
+
 // the slot after the step: the last taps - 1 inputs of [old slot | the step's rows], zeros for positions before 0
 __global__ void __launch_bounds__(256) short_conv_state_kernel(ShortConvParams p) {
   pdl_sync();
@@ -159,8 +198,22 @@ int vb_short_conv(void* d_out, int ld_out, float* d_out_f32, int ld_f32, const f
   ShortConvParams p{d_in, ld_in, d_w, d_bias, d_state, d_out, ld_out, d_out_f32, ld_f32, d_qo_indptr, d_row_req, d_pos, d_slots,
                     T, B, channels, taps, act, residual};
   const int cx = (channels + 255) / 256;
-  if (out_dtype == 1) VB_LAUNCH_PDL(short_conv_kernel<float>, dim3(cx, T), 256, 0, stream, p);
-  else VB_LAUNCH_PDL(short_conv_kernel<bf16>, dim3(cx, T), 256, 0, stream, p);
+  const dim3 rows_grid(cx, (T + SC_RPT - 1) / SC_RPT);
+  const bool f32 = out_dtype == 1;
+  if (T >= 64 && taps == 2) {
+    if (f32) VB_LAUNCH_PDL((short_conv_rows_kernel<float, 2>), rows_grid, 256, 0, stream, p);
+    else VB_LAUNCH_PDL((short_conv_rows_kernel<bf16, 2>), rows_grid, 256, 0, stream, p);
+  } else if (T >= 64 && taps == 3) {
+    if (f32) VB_LAUNCH_PDL((short_conv_rows_kernel<float, 3>), rows_grid, 256, 0, stream, p);
+    else VB_LAUNCH_PDL((short_conv_rows_kernel<bf16, 3>), rows_grid, 256, 0, stream, p);
+  } else if (T >= 64 && taps == 4) {
+    if (f32) VB_LAUNCH_PDL((short_conv_rows_kernel<float, 4>), rows_grid, 256, 0, stream, p);
+    else VB_LAUNCH_PDL((short_conv_rows_kernel<bf16, 4>), rows_grid, 256, 0, stream, p);
+  } else if (f32) {
+    VB_LAUNCH_PDL(short_conv_kernel<float>, dim3(cx, T), 256, 0, stream, p);
+  } else {
+    VB_LAUNCH_PDL(short_conv_kernel<bf16>, dim3(cx, T), 256, 0, stream, p);
+  }
   if (taps > 1) VB_LAUNCH_PDL(short_conv_state_kernel, dim3(cx, B), 256, 0, stream, p);
   return 0;
 }

@@ -360,22 +360,40 @@ __global__ void __launch_bounds__(128) sigmoid_attn_mma_kernel(SigmoidAttnParams
       key_off[tid] = off;
     }
     __syncthreads();
-    for (int i = tid; i < SM_KEYS * (D8 + V8); i += 128) {
-      const int kk = i / (D8 + V8), j = i - kk * (D8 + V8);
-      const bool is_k = j < D8;
-      const int c = (is_k ? j : j - D8) * 8, n = is_k ? D : V;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (key_id[kk] >= 0) {
-        const size_t e = (static_cast<size_t>(key_off[kk]) * p.G + g) * n + c;
-        if (c0 + kk < nb_max) {
-          const float* src = (is_k ? p.kp : p.vp) + e;
-          const float4 a = *reinterpret_cast<const float4*>(src), bq = *reinterpret_cast<const float4*>(src + 4);
-          v = make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(bq.x, bq.y), pack_bf16(bq.z, bq.w));
-        } else {
-          v = *reinterpret_cast<const uint4*>((is_k ? kc : vc) + e);
+    // 16-byte pieces of the chunk's key and value rows, eight per thread at a time: all loads of a batch are issued before the
+    // first store (a load behind a shared-memory store would wait for it)
+    const int n_pieces = SM_KEYS * (D8 + V8);
+    for (int i0 = tid; i0 < n_pieces; i0 += 128 * 8) {
+      uint4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = i0 + u * 128;
+        v[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (i < n_pieces) {
+          const int kk = i / (D8 + V8), j = i - kk * (D8 + V8);
+          const bool is_k = j < D8;
+          const int c = (is_k ? j : j - D8) * 8, n = is_k ? D : V;
+          if (key_id[kk] >= 0) {
+            const size_t e = (static_cast<size_t>(key_off[kk]) * p.G + g) * n + c;
+            if (c0 + kk < nb_max) {
+              const float* src = (is_k ? p.kp : p.vp) + e;
+              const float4 a = __ldg(reinterpret_cast<const float4*>(src)), bq = __ldg(reinterpret_cast<const float4*>(src + 4));
+              v[u] = make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(bq.x, bq.y), pack_bf16(bq.z, bq.w));
+            } else {
+              v[u] = __ldg(reinterpret_cast<const uint4*>((is_k ? kc : vc) + e));
+            }
+          }
         }
       }
-      *reinterpret_cast<uint4*>((is_k ? Ks + kk * QLD : Vs + kk * VLD) + c) = v;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = i0 + u * 128;
+        if (i < n_pieces) {
+          const int kk = i / (D8 + V8), j = i - kk * (D8 + V8);
+          const bool is_k = j < D8;
+          *reinterpret_cast<uint4*>((is_k ? Ks + kk * QLD : Vs + kk * VLD) + (is_k ? j : j - D8) * 8) = v[u];
+        }
+      }
     }
     __syncthreads();
     if (!active) continue;
