@@ -278,6 +278,13 @@ __global__ void __launch_bounds__(SA_THREADS) sigmoid_attn_kernel(SigmoidAttnPar
 // back as the A operand of O += P V (values read through transposing ldmatrix).
 constexpr int SM_KEYS = 64;
 
+// sigmoid(cap(s) + bias) from exponentials of the fast unit (relative error ~1e-6: below the bf16 rounding the weight gets as an
+// mma operand): cap tanh(s / cap) = cap - 2 cap / (exp(2 s / cap) + 1), sigmoid(x) = 1 / (1 + exp(-x)); both saturate cleanly
+__device__ __forceinline__ float sa_fast_weight(float s, float cap, float inv_cap2, float bias) {
+  if (cap > 0.f) s = cap - __fdividef(2.f * cap, __expf(s * inv_cap2) + 1.f);
+  return __fdividef(1.f, 1.f + __expf(-(s + bias)));
+}
+
 template <int NV>
 __global__ void __launch_bounds__(128) sigmoid_attn_mma_kernel(SigmoidAttnParams p) {
   extern __shared__ __align__(16) unsigned char sm_raw[];
@@ -288,6 +295,7 @@ __global__ void __launch_bounds__(128) sigmoid_attn_mma_kernel(SigmoidAttnParams
   bf16* Vs = Ks + SM_KEYS * QLD;                                  // [SM_KEYS][VLD]
   long long* key_off = reinterpret_cast<long long*>(Vs + SM_KEYS * VLD);
   int* key_id = reinterpret_cast<int*>(key_off + SM_KEYS);
+  int* see = key_id + SM_KEYS;                                    // [SM_KEYS][2]: the first and last position that sees the key
   pdl_sync();
   const int R = p.H / p.G, nh = p.heads_per_cta, wph = 4 / nh;    // warps per head
   const int hc_n = (R + nh - 1) / nh;
@@ -336,10 +344,8 @@ __global__ void __launch_bounds__(128) sigmoid_attn_mma_kernel(SigmoidAttnParams
   const bf16* vc = static_cast<const bf16*>(p.v_cache);
   const float bias = (p.head_bias && my_h < nh_eff) ? p.head_bias[h0 + my_h] : 0.f;
   const int ra = my_rb + (lane >> 2), psa = p_first + ra, psb = psa + 8;
-  int nba, loa, nbb, lob;
-  sa_range(p, psa, nba, loa);
-  sa_range(p, psb, nbb, lob);
-  const bool va = ra < nrows, vb_ = ra + 8 < nrows;
+  const int ps_a = ra < nrows ? psa : -1, ps_b = ra + 8 < nrows ? psb : -1;      // (-1: no such row; it sees nothing)
+  const float inv_cap2 = p.cap > 0.f ? 2.f / p.cap : 0.f;
   for (int c0 = it0; c0 < it1; c0 += SM_KEYS) {
     __syncthreads();
     if (tid < SM_KEYS) {
@@ -358,6 +364,15 @@ __global__ void __launch_bounds__(128) sigmoid_attn_mma_kernel(SigmoidAttnParams
       }
       key_id[tid] = id;
       key_off[tid] = off;
+      // a token j is seen from j to j + window - 1, a pooled block from the first position whose window lies wholly behind it
+      int from = 0x7fffffff, to = -1;
+      if (id >= 0) {
+        const bool pooled = it < nb_max;
+        from = pooled ? id * p.pool + p.pool - 1 + p.window : id;
+        to = (pooled || p.window <= 0) ? 0x7fffffff : id + p.window - 1;
+      }
+      see[2 * tid] = from;
+      see[2 * tid + 1] = to;
     }
     __syncthreads();
     // 16-byte pieces of the chunk's key and value rows, eight per thread at a time: all loads of a batch are issued before the
@@ -414,19 +429,13 @@ __global__ void __launch_bounds__(128) sigmoid_attn_mma_kernel(SigmoidAttnParams
     bool any = false;
 #pragma unroll
     for (int nt = 0; nt < SM_KEYS / 8; ++nt) {
+      const int4 ft = *reinterpret_cast<const int4*>(see + 2 * (nt * 8 + (lane & 3) * 2));      // (from, to) of the lane's two keys
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int col = nt * 8 + (lane & 3) * 2 + (e & 1);
-        const int id = key_id[col];
-        const bool pooled = c0 + col < nb_max, second = e >= 2;
-        const int ps = second ? psb : psa;
-        const bool seen = id >= 0 && (second ? vb_ : va) &&
-                          (pooled ? id < (second ? nbb : nba) : (id >= (second ? lob : loa) && id <= ps));
+        const int ps = e >= 2 ? ps_b : ps_a, from = (e & 1) ? ft.z : ft.x, to = (e & 1) ? ft.w : ft.y;
         float w = 0.f;
-        if (seen) {
-          float sc = S[nt][e] * p.scale;
-          if (p.cap > 0.f) sc = p.cap * tanhf(sc / p.cap);
-          w = 1.f / (1.f + expf(-(sc + bias)));
+        if (ps >= from && ps <= to) {
+          w = sa_fast_weight(S[nt][e] * p.scale, p.cap, inv_cap2, bias);
           any = true;
         }
         S[nt][e] = w;
@@ -558,7 +567,7 @@ int vb_sigmoid_attn(void* d_out, int ld_out, const void* d_q, const void* d_k_ca
                       d_page_indices, d_qo_indptr, d_tile_req, d_tile_row0, d_row_list, items, H, G, dim, vdim, page_size, window,
                       pool, pool > 0 ? (page_size + pool - 1) / pool : 0, scale, cap, out_scale, tile_rows, hpc, 1};
   const size_t smem = mma ? static_cast<size_t>(64 + SM_KEYS) * (dim + 8) * 2 + static_cast<size_t>(SM_KEYS) * (vdim + 8) * 2 +
-                                SM_KEYS * (sizeof(long long) + sizeof(int))
+                                SM_KEYS * (sizeof(long long) + 3 * sizeof(int))
                           : (static_cast<size_t>(SA_ROWS) * hpc * (dim + vdim) + static_cast<size_t>(SA_KEYS) * (dim + 1 + vdim)) * sizeof(float) +
                                 SA_KEYS * (sizeof(long long) + sizeof(int));
   VB_CHECK_ARG(smem <= static_cast<size_t>(VB_MAX_DYN_SMEM), "vb_sigmoid_attn: head sizes need %zu bytes of shared memory", smem);
@@ -567,7 +576,7 @@ int vb_sigmoid_attn(void* d_out, int ld_out, const void* d_q, const void* d_k_ca
   int splits = 1;
   if (!tiled && d_part && max_keys > 0) {
     const int chunks = (max_keys + chunk_keys - 1) / chunk_keys;
-    int want = 296 / (items * gy > 0 ? items * gy : 1);
+    int want = (mma ? 592 : 296) / (items * gy > 0 ? items * gy : 1);
     if (want > 16) want = 16;
     if (want > chunks / 2) want = chunks / 2;
     while (want > 1 && static_cast<long long>(want) * items * H * vdim > part_floats) --want;
