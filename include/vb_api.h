@@ -684,7 +684,7 @@ int vb_moe_combine(float* d_y, const float* d_expert_out, const float* d_shared_
  *   the fp32 pooled caches [pages][ceil(page / pool)][nk] / [..][nv] (block b sits in the page of position b * pool, at
  *   (b * pool mod page) / pool).
  * vb_sigmoid_attn: out[t][h * vdim ..] = out_scale * sum_j sigmoid(cap(q . k_j * scale) + head_bias[h]) v_j over the window's
- *   tokens and the pooled blocks wholly before the window (cap(s) = cap * tanh(s / cap) when cap > 0).  Tiles (d_tile_req
+ *   tokens and the pooled blocks entirely older than the window (cap(s) = cap * tanh(s / cap) when cap > 0).  Tiles (d_tile_req
  *   != NULL: rows d_tile_row0[i] .. of request d_tile_req[i], tile_rows each) or single rows (d_row_list, or rows 0 .. n_rows);
  *   d_part (optional, single rows): scratch for dealing a row's keys to several CTAs, max_keys the most keys a row can see.
  * vb_selective_scan / _tiled: S[c][n] = exp(dt A[c][n]) S[c][n] + dt x[c] B[n], y[c] = sum_n S[c][n] C[n] + D[c] x[c],

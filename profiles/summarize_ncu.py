@@ -20,7 +20,7 @@ KEEP = ["Kernel Name", "launch__grid_size", "launch__block_size", "gpu__time_dur
 out = subprocess.run(["ncu", "-i", sys.argv[1], "--page", "raw", "--csv"], capture_output=True, text=True).stdout
 rows = list(csv.reader(io.StringIO(out)))
 hdr, units, data = rows[0], rows[1], rows[2:]
-print(f"# ncu --set full --clock-control none --import-source on (cold cache, serialised launches): {len(data)} captured launches")
+print(f"# ncu --set full --clock-control none (cold cache, serialised launches): {len(data)} captured launches")
 for k in KEEP:
     for i, h in enumerate(hdr):
         if h == k or (k.startswith("smsp__pcsamp") and h == k):

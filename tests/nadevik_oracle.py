@@ -97,7 +97,7 @@ def window_keys(i: int, size: int) -> List[int]:
 
 
 def pooled_blocks(i: int, size: int, pool: int) -> List[int]:
-    """Blocks b (positions b pool .. b pool + pool - 1) that lie wholly before position i's window."""
+    """Blocks b (positions b pool .. b pool + pool - 1) that are entirely older than position i's window."""
     if pool <= 0 or size <= 0:
         return []
     out, b = [], 0
@@ -111,7 +111,7 @@ def pooled_blocks(i: int, size: int, pool: int) -> List[int]:
 def sigmoid_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, bias: torch.Tensor, scale: float, cap: float,
                    size: int, pool: int) -> torch.Tensor:
     """q [T, H, D], k [T, G, D], v [T, G, V] of ONE sequence from position 0 -> [T, H, V]: position i weighs the tokens of its
-    window and the means of the blocks wholly before it by sigmoid(capped score + bias[head]); nothing is normalised."""
+    window and the means of the blocks entirely older than it by sigmoid(capped score + bias[head]); nothing is normalised."""
     T, H, _ = q.shape
     G, V = k.shape[1], v.shape[2]
     out = torch.zeros(T, H, V, dtype=F64)

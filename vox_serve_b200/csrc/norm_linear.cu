@@ -80,7 +80,7 @@ __global__ void rmsnorm2_kernel(OT* __restrict__ out1, OT* __restrict__ out2, co
   }
 }
 
-// Norm on a sublayer's OUTPUT only, in place on the fp32 stream: x[t] += y[t] / sqrt(mean(y[t]^2) + eps) * w, and (optional)
+// Stacks that norm what a sublayer returns instead of what it reads; in place on the fp32 stream: x[t] += y[t] / sqrt(mean(y[t]^2) + eps) * w, and (optional)
 // out[t] = x[t] in the compute type: what a following sublayer reads when it takes the stream itself, un-normed.
 template <typename OT>
 __global__ void __launch_bounds__(256) rms_postnorm_residual_kernel(float* __restrict__ x, const float* __restrict__ y,

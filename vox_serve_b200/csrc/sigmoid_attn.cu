@@ -4,9 +4,9 @@
 //   o_i   = out_scale * sum_j sigmoid(s_ij + bias[head]) * v_j
 //
 // where j runs over the tokens of the window (0 <= i - j < window; window <= 0: all earlier tokens) and, with pool = P > 0,
-// over one pooled key / value per block of P positions that lies wholly before the window (block b = positions bP .. bP + P - 1
-// is seen by i when bP + P - 1 <= i - window): the mean of the block's cached keys / values.  Tokens and blocks are treated
-// alike.  Grouped heads: query head h reads key/value head h / (H / G).  Queries, the page cache and the output take the
+// over one pooled key / value per block of P positions that ended before the window began (block b = positions bP .. bP + P - 1
+// is seen by i when bP + P - 1 <= i - window): the mean of the block's cached keys / values.  A pooled entry is scored, capped,
+// biased and weighted exactly as a token is.  Grouped heads: query head h reads key/value head h / (H / G).  Queries, the page cache and the output take the
 // compute type; pooled blocks are kept in fp32 in a cache of their own; scores, weights and sums are fp32.
 //
 // Because nothing is normalised, partial sums over disjoint key ranges simply add up: a row's keys can be dealt to several

@@ -20,7 +20,11 @@ each followed (sequential form) by ``x += LayerNorm(y)`` fused with the LayerNor
 A third block form, ``gated`` (pre-norm, ``x += sigmoid(W_r h + b) * sublayer(h)``, scalar RMS norms, optionally a span of
 layers run several times with a cache or state per pass), carries three more mixers -- latent attention with direct queries
 and a shared rotated key part, attention with two score maps per head restricted to chunks, minGRU -- and a clamped gated
-feed-forward (``_forward_gated`` at the end of this file).
+feed-forward (``_forward_gated``).  A fourth, ``post`` (what a sublayer returns is normed, what it reads is not: the sublayers take the stream
+itself -- the mixer through a short causal input convolution with state), carries latent attention in a window with a gate per
+output value and rows that layers may share, and a pair of mixers side by side -- attention whose weights are sigmoids over a
+window plus pooled blocks, and a selective scan -- with a group-limited softmax router over clamped gated experts, a hashed
+token-pair embedding and a tied head (``_forward_post`` at the end of this file).
 
 Precision: ``dtype`` bfloat16 keeps projections' operands, q / k / v, the page cache and the attention output in bf16 with
 fp32 accumulation; norms, softmax, router, residual, recurrent state, decays and the lightning path after its projection
@@ -145,7 +149,7 @@ class PooledSigmoidAttentionConfig:
     keys.  q, k, v pass a short causal convolution (conv taps; 0 / 1: none) right after their projection; q and k are then
     RMS-normed over their WHOLE projection (all heads at once, one weight per coordinate).  Scores are soft-capped
     (softcap * tanh(score / softcap); 0: no cap).  A position sees the tokens of its window and, with pool = P > 0, one mean
-    key / value per block of P positions that lies wholly before the window."""
+    key / value per block of P positions whose last position is older than the window's oldest."""
     heads: int
     kv_heads: int
     dim: int
@@ -263,7 +267,7 @@ class HybridConfig:
     layers: List[HybridLayerConfig]
     block: str = "sequential"             # "sequential": x += LN(mixer(LN x)); x += LN(ff(LN x)).  "parallel": x += m * (mixer(n1 x) + ff(n2 x))
     #                                       "gated": pre-norm, x += sigmoid(W_r h + b) * sublayer(h) with h = norm(x), mixer then ff
-    #                                       "post": norm on the sublayer's output only, x += norm(sublayer(x)); the sublayers
+    #                                       "post": x += norm(sublayer(x)): only what a sublayer returns is normed; the sublayers
     #                                       read the stream itself (the mixer through the input convolution, if any)
     norm: str = "layernorm"               # "layernorm" (weight and bias) | "rmsnorm" (weight) | "rmsnorm_scalar" (one number) |
     #                                       "rmsnorm_offset" (the stored weight is an offset from one: x / rms * (1 + w))
@@ -382,7 +386,7 @@ class HybridWeights:
             def norm(name):                                        # noqa: F811  (one number, kept as a constant vector)
                 return vec(name).reshape(1).expand(cfg.width).contiguous(), None
         elif cfg.norm == "rmsnorm_offset":
-            def norm(name):                                        # noqa: F811  (stored around zero: the weight is 1 + w, in fp32)
+            def norm(name):                                        # noqa: F811  (the checkpoint holds w, the weight is 1 + w, formed in fp32)
                 return (vec(name) + 1.0).contiguous(), None
         self._gate_up = gate_up
         self.embed = mat("embed")

@@ -12,7 +12,7 @@ token, token) pair is added; the output head is the embedding table itself.
       a pair of mixers side by side on the same input, left_scale * left + right_scale * right:
         left -- grouped-head attention without rotation: short causal convolutions on q, k, v right after their projection,
           RMS norm of q and of k over the whole projection, soft-capped scores, a sliding window plus one pooled (mean) key /
-          value per block of positions wholly before the window, weights sigmoid(score + bias of the head) that are not
+          value per block of positions entirely older than the window, weights sigmoid(score + bias of the head) that are not
           normalised over the keys;
         right -- a selective scan (Mamba form) over an fp32 state per request.
   * feed-forward: none, or a mixture of clamped gated experts, down(g * sigmoid(1.702 g) * (u + 1)) with g = min(gate h,

@@ -1483,7 +1483,7 @@ def sigmoid_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
                  rows: Optional[Tuple[torch.Tensor, int]] = None, scratch: Optional[torch.Tensor] = None,
                  max_keys: int = 0) -> torch.Tensor:
     """out[t, h * vdim : (h + 1) * vdim] = out_scale * sum_j sigmoid(cap * tanh(q . k_j * scale / cap) + head_bias[h]) v_j over
-    the tokens of the window and the pooled blocks wholly before it (no normalisation over the keys).  q [T, H * dim], caches
+    the tokens of the window and the pooled blocks entirely older than it (no normalisation over the keys).  q [T, H * dim], caches
     [pages, page, G, dim / vdim] (bf16 or fp32, as q and out); out a view [T, >= H * vdim] with any row stride.  tiles =
     (qo_indptr, tile_req, tile_row0, n_tiles, tile_rows): the rows of those tiles; else the rows listed in ``rows`` (or all T).
     scratch (fp32) + max_keys: lets a small step deal a row's keys to several CTAs."""

@@ -1,10 +1,11 @@
-"""Worker for text-only LMs on the hybrid engine (model/bobavik.py, model/razevik.py): the same five scheduler-facing methods, page pool,
+"""Worker for text-only LMs on the hybrid engine (model/bobavik.py, model/razevik.py, model/fovunex.py, model/nadevik.py): the same five scheduler-facing methods, page pool,
 batch slots, packed staging buffer, sampled-id ring and decode CUDA graphs as ``ModelWorker``, with three differences.
 
   * Prompts are fed in portions.  A request carries ``pending_tokens`` (the rest of its prompt, or continuation tokens a
     client supplies); a step takes ``step_tokens`` of them (default: ``prefill_chunk_tokens``, or all), so portions of
     prompts run in one batch beside single decoded tokens.  Positions count from 0 without gaps.
-  * A request owns a state slot besides its pages: the recurrent layers keep one fp32 state per slot (``HybridCache``).
+  * A request owns a state slot besides its pages: the recurrent layers keep one fp32 state per slot (``HybridCache``), and so
+    do short convolutions (their last inputs) and a token-pair embedding (the last token).
     The slot index is the request's batch slot, so slot-resident sampling state and recurrent state share one pool.  Pages
     and slots go back to their pools in ``free_kv_cache`` and are handed out again without clearing: the kernels start a
     request at position 0 from a zero state, and no page is read before it is written.
