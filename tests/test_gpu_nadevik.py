@@ -406,7 +406,7 @@ def test_sigmoid_attention_window_and_pool_edges(dtype, window, pool, page):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype,H,G,D,V", [(F32, 10, 2, 24, 40), (BF16, 10, 2, 24, 40), (BF16, 8, 2, 32, 48), (BF16, 6, 3, 64, 128),
-                                           (BF16, 3, 3, 16, 16), (BF16, 4, 1, 128, 64)])
+                                           (BF16, 3, 3, 16, 16), (BF16, 4, 1, 128, 64), (BF16, 6, 2, 32, 32), (BF16, 5, 1, 16, 32)])
 def test_sigmoid_attention_far_keys_batches_and_out_scale(dtype, H, G, D, V):
     """three requests of unequal lengths in one launch (tiles and single rows), positions hundreds of keys and dozens of pages
     from their hot key, an output scale, more heads per group than a CTA takes at once; the plain kernel (float32, odd sizes)

@@ -39,6 +39,7 @@ struct ShortConvParams {
   const int32_t* pos;
   const int32_t* slots;
   int T, B, C, taps, act, residual;
+  int single_inline;      // requests that bring one row had their slot shifted by the convolution kernel itself
 };
 
 template <typename CT> __device__ __forceinline__ void sc_store(void* out, size_t i, float v);
@@ -63,9 +64,26 @@ __global__ void __launch_bounds__(256) short_conv_kernel(ShortConvParams p) {
     acc = fmaf(w[j], u, acc);
   }
   if (p.act == 1) acc = acc / (1.f + expf(-acc));
-  if (p.residual) acc += p.in[static_cast<size_t>(t) * p.ld_in + c];
+  const float cur = p.in[static_cast<size_t>(t) * p.ld_in + c];
+  if (p.residual) acc += cur;
   if (p.out) sc_store<CT>(p.out, static_cast<size_t>(t) * p.ld_out + c, acc);
   if (p.out_f32) p.out_f32[static_cast<size_t>(t) * p.ld_f32 + c] = acc;
+  // a request that brings exactly one row: this thread is the slot's only reader for the channel, so it also shifts the slot
+  // (zeros for positions before 0) -- the second kernel leaves such requests alone, and steps made of them skip it
+  if (K > 0 && p.qo_indptr[b + 1] - p.qo_indptr[b] == 1) {
+    float* sw = p.state + (static_cast<size_t>(p.slots[b]) * K) * p.C + c;
+    float keep[SC_MAX_TAPS];
+#pragma unroll
+    for (int i = 0; i < SC_MAX_TAPS; ++i) {
+      if (i >= K) break;
+      keep[i] = i + 1 < K ? ((ps - K + i + 1 >= 0) ? sw[static_cast<size_t>(i + 1) * p.C] : 0.f) : cur;
+    }
+#pragma unroll
+    for (int i = 0; i < SC_MAX_TAPS; ++i) {
+      if (i >= K) break;
+      sw[static_cast<size_t>(i) * p.C] = keep[i];
+    }
+  }
 }
 
 // Long steps, 2 to 4 taps: a thread computes SC_RPT consecutive rows of its channel from one read of the rows' inputs (the
@@ -114,6 +132,7 @@ __global__ void __launch_bounds__(256) short_conv_state_kernel(ShortConvParams p
   if (c >= p.C) return;
   const int r0 = p.qo_indptr[b], n = p.qo_indptr[b + 1] - r0, K = p.taps - 1;
   if (n <= 0 || K <= 0) return;
+  if (n == 1 && p.single_inline) return;        // (shifted by the row's own thread)
   const int p0 = p.pos[r0];
   float* st = p.state + (static_cast<size_t>(p.slots[b]) * K) * p.C + c;
   float keep[SC_MAX_TAPS];
@@ -195,8 +214,9 @@ int vb_short_conv(void* d_out, int ld_out, float* d_out_f32, int ld_f32, const f
   VB_CHECK_ARG(channels > 0 && taps >= 1 && taps <= SC_MAX_TAPS && (act == 0 || act == 1) && ld_in >= channels,
                "vb_short_conv: channels %d, taps %d (1..%d), act %d", channels, taps, SC_MAX_TAPS, act);
   if (T <= 0 || B <= 0) return 0;
+  const bool rows_form = T >= 64 && taps >= 2 && taps <= 4;
   ShortConvParams p{d_in, ld_in, d_w, d_bias, d_state, d_out, ld_out, d_out_f32, ld_f32, d_qo_indptr, d_row_req, d_pos, d_slots,
-                    T, B, channels, taps, act, residual};
+                    T, B, channels, taps, act, residual, rows_form ? 0 : 1};
   const int cx = (channels + 255) / 256;
   const dim3 rows_grid(cx, (T + SC_RPT - 1) / SC_RPT);
   const bool f32 = out_dtype == 1;
@@ -214,7 +234,8 @@ int vb_short_conv(void* d_out, int ld_out, float* d_out_f32, int ld_f32, const f
   } else {
     VB_LAUNCH_PDL(short_conv_kernel<bf16>, dim3(cx, T), 256, 0, stream, p);
   }
-  if (taps > 1) VB_LAUNCH_PDL(short_conv_state_kernel, dim3(cx, B), 256, 0, stream, p);
+  // (T == B: every request brings one row, and the convolution kernel has shifted every slot)
+  if (taps > 1 && !(p.single_inline && T == B)) VB_LAUNCH_PDL(short_conv_state_kernel, dim3(cx, B), 256, 0, stream, p);
   return 0;
 }
 

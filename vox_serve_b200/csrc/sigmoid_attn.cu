@@ -85,10 +85,19 @@ __global__ void __launch_bounds__(256) pool_blocks_kernel(float* __restrict__ kp
   const float inv = 1.f / static_cast<float>(P);
   for (int e = threadIdx.x; e < nk + nv; e += 256) {
     float s = 0.f;
-    for (int i = 0; i < P; ++i) {
-      const int ps = first + i;
-      const size_t tok = static_cast<size_t>(pages[ps / page_size]) * page_size + ps % page_size;
-      s += e < nk ? sa_to_f(k_cache[tok * nk + e]) : sa_to_f(v_cache[tok * nv + e - nk]);
+    for (int i0 = 0; i0 < P; i0 += 8) {             // eight positions' loads in flight, summed in position order
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int ps = first + i0 + u;
+        v[u] = 0.f;
+        if (i0 + u < P) {
+          const size_t tok = static_cast<size_t>(pages[ps / page_size]) * page_size + ps % page_size;
+          v[u] = e < nk ? sa_to_f(k_cache[tok * nk + e]) : sa_to_f(v_cache[tok * nv + e - nk]);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) s += v[u];
     }
     if (e < nk) kp[dst * nk + e] = s * inv;
     else vp[dst * nv + e - nk] = s * inv;

@@ -522,6 +522,8 @@ class HybridWeights:
                         (m.rotary.key() if m.rotary else None)):
                     raise VoxB200Error(f"layer {i}: kv_from {m.kv_from} must name an earlier latent-attention layer that projects "
                                        "its own latents, of the same rank, rotated part and rotation")
+            if m.value_gate and (p + "mix.g") not in sd:       # (a checkpoint without the gate's matrix: no gate)
+                m.value_gate = False
             dq = m.dim + m.rot_dim
             parts = [mat(p + "mix.q")] + ([mat(p + "mix.dkv")] if own else []) + ([mat(p + "mix.g")] if m.value_gate else [])
             uk, uv, o = mat(p + "mix.uk"), mat(p + "mix.uv"), mat(p + "mix.o")
