@@ -83,21 +83,14 @@ __global__ void __launch_bounds__(256) pool_blocks_kernel(float* __restrict__ kp
   const int first = blk * P;
   const size_t dst = static_cast<size_t>(pages[first / page_size]) * pool_slots + (first % page_size) / P;
   const float inv = 1.f / static_cast<float>(P);
-  for (int e = threadIdx.x; e < nk + nv; e += 256) {
+  // (grid.z deals the block's values to CTAs: a thread forms one mean, in position order)
+  for (int e = blockIdx.z * 256 + threadIdx.x; e < nk + nv; e += gridDim.z * 256) {
     float s = 0.f;
-    for (int i0 = 0; i0 < P; i0 += 8) {             // eight positions' loads in flight, summed in position order
-      float v[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int ps = first + i0 + u;
-        v[u] = 0.f;
-        if (i0 + u < P) {
-          const size_t tok = static_cast<size_t>(pages[ps / page_size]) * page_size + ps % page_size;
-          v[u] = e < nk ? sa_to_f(k_cache[tok * nk + e]) : sa_to_f(v_cache[tok * nv + e - nk]);
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < 8; ++u) s += v[u];
+#pragma unroll 4
+    for (int i = 0; i < P; ++i) {
+      const int ps = first + i;
+      const size_t tok = static_cast<size_t>(pages[ps / page_size]) * page_size + ps % page_size;
+      s += e < nk ? sa_to_f(k_cache[tok * nk + e]) : sa_to_f(v_cache[tok * nv + e - nk]);
     }
     if (e < nk) kp[dst * nk + e] = s * inv;
     else vp[dst * nv + e - nk] = s * inv;
@@ -537,7 +530,7 @@ int vb_pool_blocks(float* d_kp, float* d_vp, const void* d_k_cache, const void* 
   VB_CHECK_ARG(pool > 0 && page_size > 0 && nk > 0 && nv > 0, "vb_pool_blocks: bad sizes");
   if (T <= 0 || B <= 0) return 0;
   const int slots = (page_size + pool - 1) / pool;
-  dim3 grid(T / pool + 1, B);
+  dim3 grid(T / pool + 1, B, (nk + nv + 255) / 256 < 16 ? (nk + nv + 255) / 256 : 16);
   if (dtype == 1)
     VB_LAUNCH_PDL(pool_blocks_kernel<float>, grid, 256, 0, stream, d_kp, d_vp, static_cast<const float*>(d_k_cache),
                   static_cast<const float*>(d_v_cache), d_qo_indptr, d_pos, d_page_indptr, d_page_indices, page_size, pool, slots, nk, nv);
