@@ -675,7 +675,8 @@ int vb_moe_combine(float* d_y, const float* d_expert_out, const float* d_shared_
  *   token before a step's first row comes from d_prev_tok[slot], which then takes the step's last token.
  * vb_short_conv: causal convolution over time per channel of the fp32 columns d_in[t][0 .. channels), weights fp32
  *   [channels][taps] (last column: the current token), optional bias, act 1 = silu, residual != 0: the input is added to the
- *   result; d_state [slots][taps - 1][channels] holds a request's last inputs and is advanced by the step (two launches).
+ *   result; d_state [slots][taps - 1][channels] holds a request's last inputs and is advanced by the step (by the convolution
+ *   kernel itself for requests that bring one row, by a second launch for the others).
  *   Output in the compute type (d_out) and / or fp32 (d_out_f32).
  * vb_cast_rows: d_out [T][n] (dense, compute type) = d_in[t][0 .. n) (fp32 rows of stride ld_in).
  * vb_qk_norm_append: tail of a (q | k | v) projection: q and k RMS-normed over their whole width nq / nk with per-coordinate

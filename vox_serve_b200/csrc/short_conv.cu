@@ -6,9 +6,10 @@
 //
 // u is a column range of fp32 rows (the residual stream, or the rows of a fused projection), so several convolutions over
 // neighbouring columns of one projection run as ONE call with their weights stacked.  A request's last taps - 1 inputs live
-// in an fp32 slot [taps - 1][C]; rows whose taps reach before the step's first row read them from there.  The slot is
-// rewritten by a second kernel after the outputs (every thread owns one (request, channel) and reads all it needs before it
-// writes), and a slot's content is ignored wherever a tap reaches before position 0, so slots are reused without clearing.
+// in an fp32 slot [taps - 1][C]; rows whose taps reach before the step's first row read them from there.  A request that
+// brings one row has its slot shifted by that row's own thread; the slots of the others are rewritten by a second kernel after
+// the outputs (every thread owns one (request, channel) and reads all it needs before it writes).  A slot's content is ignored
+// wherever a tap reaches before position 0, so slots are reused without clearing.
 // Every output is one fp32 FMA chain over the taps in the same order, whatever the step's cut.
 //
 //   vb_pair_hash_rows   row[t] = (prev * mul_prev + id * mul_cur) mod buckets, `buckets` itself for a request's first token;

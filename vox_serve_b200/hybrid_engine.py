@@ -1418,6 +1418,7 @@ class HybridEngine:
         for i, L in enumerate(cfg.layers):
             lw = w.layers[i]
             if cfg.input_conv:
+                # (a convolution of one tap keeps no inputs: any fp32 tensor stands in for its slot)
                 ops.short_conv(x, lw["canon"], None, self.cache.conv.get((i, "in"), self.x), s.qo_indptr, s.row_req, s.pos,
                                s.slots, s.B, out=h, residual=True)
             else:
